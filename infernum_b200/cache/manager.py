@@ -132,12 +132,15 @@ class CacheManager:
                 lc.group, lc.page_size, lc.num_pages = g, self.page_size, pages + 1
                 if device is not None:
                     shape = (pages + 1, need.paged.kv_heads, self.page_size, need.paged.head_dim)
+                    v_shape = (pages + 1, need.paged.kv_heads, self.page_size, need.paged.value_dim)
                     try:
                         lc.k_pool = torch.zeros(shape, dtype=dtype, device=device)
-                        lc.v_pool = torch.zeros(shape, dtype=dtype, device=device)
+                        # (a spec without values of their own has the key pool only)
+                        lc.v_pool = torch.zeros(v_shape, dtype=dtype, device=device) \
+                            if need.paged.value_dim > 0 else None
                     except torch.cuda.OutOfMemoryError:
                         el = torch.empty((), dtype=dtype).element_size()
-                        per_page = sum(2 * n.paged.kv_heads * self.page_size * n.paged.head_dim * el
+                        per_page = sum(n.paged.elements_per_token() * self.page_size * el
                                        for n in needs if n.paged is not None and n.cache_of is None)
                         free = torch.cuda.mem_get_info(device)[0]
                         raise CacheError(
@@ -164,7 +167,7 @@ class CacheManager:
         if not 0.0 < fraction <= 1.0:
             raise CacheError("memory_fraction must be in (0, 1]")
         el = torch.empty((), dtype=dtype).element_size()
-        per_page = sum(2 * n.paged.kv_heads * self.page_size * n.paged.head_dim * el
+        per_page = sum(n.paged.elements_per_token() * self.page_size * el
                        for n in needs if n.paged is not None and n.cache_of is None)
         if per_page == 0:
             return 1
@@ -223,7 +226,7 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Cache bytes one token occupies over all groups and members."""
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * g.spec.kv_heads * g.spec.head_dim * el * len(g.positions) for g in self.groups)
+        return sum(g.spec.elements_per_token() * el * len(g.positions) for g in self.groups)
 
     def free_pages(self) -> List[int]:
         return [g.pool.num_free for g in self.groups]

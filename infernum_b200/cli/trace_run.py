@@ -37,7 +37,7 @@ def build_parser() -> argparse.ArgumentParser:
                     help="most tokens live requests hold at any time, each request's count "
                          "rounded up to a multiple of 64; the page pool is made for this many")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (divides 64)")
-    ap.add_argument("--max-live", type=int, default=8, help="request slots")
+    ap.add_argument("--max-live", type=int, default=4, help="request slots")
     ap.add_argument("--device", default="cuda:0")
     return ap
 

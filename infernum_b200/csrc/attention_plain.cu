@@ -14,9 +14,14 @@
 
 using namespace ib;
 
-#define PLAIN_MAX_REGS 8  // head sizes up to 256
-
-template <typename T>
+// Keys and values need not have the same size, nor live in different pools: a
+// value may be the first `hdv` elements of a row of `v_width` elements (for a
+// latent cache the value of a token is the first part of its key, and both
+// pointers name the one pool).  Heads of a query or output row may be further
+// apart than their size (`q_hs`, `o_hs`).
+//
+// NREG * 32 is the largest key size a build of the kernel takes.
+template <typename T, int PLAIN_MAX_REGS>
 __global__ void attention_plain_kernel(const T* __restrict__ q, int q_stride,
                                        const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                        T* __restrict__ out, int out_stride,
@@ -24,7 +29,8 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, int q_stride,
                                        const int* __restrict__ row_entry,
                                        const int* __restrict__ block_tables, int max_blocks,
                                        int nh, int nkv, int hd, int page_size, int num_pages,
-                                       int window, float scale, unsigned* __restrict__ err) {
+                                       int window, float scale, int hdv, int v_width, int q_hs, int o_hs,
+                                       unsigned* __restrict__ err) {
     const int row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -35,7 +41,7 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, int q_stride,
     const int* table = block_tables + (size_t)e * max_blocks;
 
     float qr[PLAIN_MAX_REGS], acc[PLAIN_MAX_REGS];
-    const T* qp = q + (size_t)row * q_stride + (size_t)head * hd;
+    const T* qp = q + (size_t)row * q_stride + (size_t)head * q_hs;
 #pragma unroll
     for (int i = 0; i < PLAIN_MAX_REGS; ++i) {
         const int d = lane + 32 * i;
@@ -50,9 +56,9 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, int q_stride,
             if (lane == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
             continue;
         }
-        const size_t off = (((size_t)page * nkv + g) * page_size + (j % page_size)) * hd;
-        const T* kp = k_pool + off;
-        const T* vp = v_pool + off;
+        const size_t at = ((size_t)page * nkv + g) * page_size + (j % page_size);
+        const T* kp = k_pool + at * hd;
+        const T* vp = v_pool + at * v_width;
         float part = 0.f;
 #pragma unroll
         for (int i = 0; i < PLAIN_MAX_REGS; ++i) {
@@ -67,17 +73,64 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, int q_stride,
 #pragma unroll
         for (int i = 0; i < PLAIN_MAX_REGS; ++i) {
             const int d = lane + 32 * i;
-            if (d < hd) acc[i] = acc[i] * corr + p * to_f32(vp[d]);
+            if (d < hdv) acc[i] = acc[i] * corr + p * to_f32(vp[d]);
         }
         m = m_new;
     }
-    T* op = out + (size_t)row * out_stride + (size_t)head * hd;
+    T* op = out + (size_t)row * out_stride + (size_t)head * o_hs;
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < PLAIN_MAX_REGS; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) op[d] = from_f32<T>(acc[i] * inv);
+        if (d < hdv) op[d] = from_f32<T>(acc[i] * inv);
     }
+}
+
+template <typename T, int NREG>
+static int launch_plain(const void* q, int q_stride, const void* k_pool, const void* v_pool, void* out,
+                        int out_stride, const int* positions, const int* row_entry, const int* block_tables,
+                        int max_blocks, int n_rows, int nh, int nkv, int hd, int page_size, int num_pages,
+                        int window, float scale, int hdv, int v_width, int q_hs, int o_hs, unsigned* err,
+                        cudaStream_t s) {
+    const int warps = 4;
+    dim3 grid(n_rows, (nh + warps - 1) / warps);
+    attention_plain_kernel<T, NREG><<<grid, warps * 32, 0, s>>>(
+        (const T*)q, q_stride, (const T*)k_pool, (const T*)v_pool, (T*)out, out_stride, positions, row_entry,
+        block_tables, max_blocks, nh, nkv, hd, page_size, num_pages, window, scale, hdv, v_width, q_hs, o_hs, err);
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// The general form: values of `hdv` elements in rows of `v_width`, query heads
+// `q_hs` and output heads `o_hs` elements apart.
+IB_EXPORT int ib_attention_plain_ex(const void* q, int q_stride, const void* k_pool, const void* v_pool,
+                                    void* out, int out_stride, int act_dtype, const int* positions,
+                                    const int* row_entry, const int* block_tables, int max_blocks, int n_rows,
+                                    int nh, int nkv, int hd, int page_size, int num_pages, int window,
+                                    float scale, int hdv, int v_width, int q_hs, int o_hs, unsigned* err,
+                                    void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!q || !k_pool || !v_pool || !out || !positions || !row_entry || !block_tables || !err)
+        return IB_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0 ||
+        num_pages <= 0 || hdv <= 0 || hdv > v_width || hdv > hd || q_hs < hd || o_hs < hdv)
+        return IB_ERR_BAD_ARG;
+    if (hd > 32 * 20) return IB_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+#define IB_PLAIN(T, NREG)                                                                                   \
+    return launch_plain<T, NREG>(q, q_stride, k_pool, v_pool, out, out_stride, positions, row_entry,        \
+                                 block_tables, max_blocks, n_rows, nh, nkv, hd, page_size, num_pages, window, \
+                                 scale, hdv, v_width, q_hs, o_hs, err, s)
+    if (act_dtype == 0) {
+        if (hd <= 256) IB_PLAIN(float, 8);
+        IB_PLAIN(float, 20);
+    }
+    if (act_dtype == 1) {
+        if (hd <= 256) IB_PLAIN(bf16, 8);
+        IB_PLAIN(bf16, 20);
+    }
+#undef IB_PLAIN
+    return IB_ERR_UNSUPPORTED;
 }
 
 IB_EXPORT int ib_attention_plain(const void* q, int q_stride, const void* k_pool,
@@ -86,28 +139,7 @@ IB_EXPORT int ib_attention_plain(const void* q, int q_stride, const void* k_pool
                                  const int* block_tables, int max_blocks, int n_rows, int nh,
                                  int nkv, int hd, int page_size, int num_pages, int window,
                                  float scale, unsigned* err, void* stream) {
-    if (n_rows <= 0) return IB_OK;
-    if (!q || !k_pool || !v_pool || !out || !positions || !row_entry || !block_tables || !err)
-        return IB_ERR_BAD_ARG;
-    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0 ||
-        num_pages <= 0)
-        return IB_ERR_BAD_ARG;
-    if (hd > 32 * PLAIN_MAX_REGS) return IB_ERR_TOO_LARGE;
-    cudaStream_t s = (cudaStream_t)stream;
-    const int warps = 4;
-    dim3 grid(n_rows, (nh + warps - 1) / warps);
-    if (act_dtype == 0)
-        attention_plain_kernel<float><<<grid, warps * 32, 0, s>>>(
-            (const float*)q, q_stride, (const float*)k_pool, (const float*)v_pool, (float*)out,
-            out_stride, positions, row_entry, block_tables, max_blocks, nh, nkv, hd, page_size,
-            num_pages, window, scale, err);
-    else if (act_dtype == 1)
-        attention_plain_kernel<bf16><<<grid, warps * 32, 0, s>>>(
-            (const bf16*)q, q_stride, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
-            out_stride, positions, row_entry, block_tables, max_blocks, nh, nkv, hd, page_size,
-            num_pages, window, scale, err);
-    else
-        return IB_ERR_UNSUPPORTED;
-    IB_LAUNCH_CHECK();
-    return IB_OK;
+    return ib_attention_plain_ex(q, q_stride, k_pool, v_pool, out, out_stride, act_dtype, positions, row_entry,
+                                 block_tables, max_blocks, n_rows, nh, nkv, hd, page_size, num_pages, window,
+                                 scale, hd, hd, hd, hd, err, stream);
 }

@@ -486,16 +486,31 @@ IB_EXPORT int ib_rope_append(void* qkv, int act_dtype, int qkv_stride, const int
 }
 
 // ---------------------------------------------------------------------------
-// SwiGLU activation: out[t, i] = silu(gate_i) * up_i, x is [N, 2I].
+// Gated activation: out[t, i] = act(gate_i) * up_i, x is [N, 2I].
 // Where gate and up sit in a row of x is given by `blk`: the row is cut in
 // pieces of 2*blk values, each blk gates followed by their blk ups.  blk = I is
 // the plain layout [all gates | all ups]; blk = 64 is the layout of a product
 // whose weight rows were interleaved 64 by 64 (so that one 128-row tile of the
 // tcgen05 product holds gates and their ups).
 // ---------------------------------------------------------------------------
+// `act` chooses the activation of the gate: 0 = SiLU, g / (1 + exp(-g));
+// 1 = GELU in its tanh form, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+// With `scale` [N, n_scales] every output is also multiplied by
+// scale[row, i / cols_per_scale]: the outputs are those of n_scales experts
+// side by side and the scale is the weight the row's router gave each (0 for
+// an expert it did not choose).
+__device__ __forceinline__ float gate_act(float g, int act) {
+    if (act == 1) {
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        return 0.5f * g * (1.f + tanhf(inner));
+    }
+    return g / (1.f + expf(-g));
+}
+
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int I, int blk,
-                                size_t total) {
+__global__ void gated_act_kernel(const T* __restrict__ x, T* __restrict__ out, int I, int blk,
+                                 size_t total, int act, const float* __restrict__ scale,
+                                 int cols_per_scale, int n_scales) {
     pdl_trigger();
     pdl_wait();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -505,13 +520,15 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
     const size_t gi = row * 2 * I + (size_t)(i / blk) * 2 * blk + (i % blk);
     const float g = to_f32(x[gi]);
     const float u = to_f32(x[gi + blk]);
-    const float act = g / (1.f + expf(-g));
-    out[idx] = from_f32<T>(act * u);
+    float y = gate_act(g, act) * u;
+    if (scale) y *= scale[row * n_scales + i / cols_per_scale];
+    out[idx] = from_f32<T>(y);
 }
 
 // Eight outputs per thread with 16-byte loads and stores (I and blk multiples of 8).
-__global__ void silu_mul_vec8_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int I,
-                                     int blk, size_t total_vec) {
+__global__ void gated_act_vec8_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int I,
+                                      int blk, size_t total_vec, int act, const float* __restrict__ scale,
+                                      int cols_per_scale, int n_scales) {
     pdl_trigger();
     pdl_wait();
     const size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -524,44 +541,59 @@ __global__ void silu_mul_vec8_kernel(const bf16* __restrict__ x, bf16* __restric
     const uint4 u4 = *reinterpret_cast<const uint4*>(x + gi + blk);
     const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
     const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    // (cols_per_scale is a multiple of 8 here: the eight outputs share a scale)
+    const float sc = scale ? scale[row * n_scales + i / cols_per_scale] : 1.f;
     uint4 o4;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
-        o2[k] = __floats2bfloat162_rn(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y);
+        float a = gate_act(g.x, act) * u.x, b = gate_act(g.y, act) * u.y;
+        if (scale) { a *= sc; b *= sc; }
+        o2[k] = __floats2bfloat162_rn(a, b);
     }
     *reinterpret_cast<uint4*>(out + row * I + i) = o4;
 }
 
-IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, int I, int blk,
-                          void* stream) {
+IB_EXPORT int ib_gated_act(const void* x, void* out, int act_dtype, int n_rows, int I, int blk, int act,
+                           const float* scale, int cols_per_scale, void* stream) {
     if (n_rows <= 0) return IB_OK;
-    if (!x || !out || I <= 0 || blk <= 0 || I % blk) return IB_ERR_BAD_ARG;
+    if (!x || !out || I <= 0 || blk <= 0 || I % blk || act < 0 || act > 1) return IB_ERR_BAD_ARG;
+    if (scale && (cols_per_scale <= 0 || I % cols_per_scale)) return IB_ERR_BAD_ARG;
+    const int n_scales = scale ? I / cols_per_scale : 0;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)n_rows * I;
-    if (act_dtype == 1 && I % 8 == 0 && blk % 8 == 0 && !(((uintptr_t)x | (uintptr_t)out) & 15)) {
+    if (act_dtype == 1 && I % 8 == 0 && blk % 8 == 0 && (!scale || cols_per_scale % 8 == 0) &&
+        !(((uintptr_t)x | (uintptr_t)out) & 15)) {
         const size_t total_vec = total / 8;
-        cudaError_t le = launch_kernel(silu_mul_vec8_kernel, dim3((unsigned)((total_vec + 255) / 256)),
-                                       dim3(256), 0, s, (const bf16*)x, (bf16*)out, I, blk, total_vec);
+        cudaError_t le = launch_kernel(gated_act_vec8_kernel, dim3((unsigned)((total_vec + 255) / 256)),
+                                       dim3(256), 0, s, (const bf16*)x, (bf16*)out, I, blk, total_vec, act, scale,
+                                       cols_per_scale, n_scales);
         if (le != cudaSuccess) return (int)le;
         IB_LAUNCH_CHECK();
         return IB_OK;
     }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (act_dtype == 0) {
-        cudaError_t le = launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s,
-                                       (const float*)x, (float*)out, I, blk, total);
+        cudaError_t le = launch_kernel(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, s,
+                                       (const float*)x, (float*)out, I, blk, total, act, scale, cols_per_scale,
+                                       n_scales);
         if (le != cudaSuccess) return (int)le;
     } else if (act_dtype == 1) {
-        cudaError_t le = launch_kernel(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s,
-                                       (const bf16*)x, (bf16*)out, I, blk, total);
+        cudaError_t le = launch_kernel(gated_act_kernel<bf16>, dim3(blocks), dim3(256), 0, s,
+                                       (const bf16*)x, (bf16*)out, I, blk, total, act, scale, cols_per_scale,
+                                       n_scales);
         if (le != cudaSuccess) return (int)le;
     } else {
         return IB_ERR_UNSUPPORTED;
     }
     IB_LAUNCH_CHECK();
     return IB_OK;
+}
+
+IB_EXPORT int ib_silu_mul(const void* x, void* out, int act_dtype, int n_rows, int I, int blk,
+                          void* stream) {
+    return ib_gated_act(x, out, act_dtype, n_rows, I, blk, 0, nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -17,7 +17,12 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw,
-                  TC* __restrict__ C, int ldc, int M, int N, int K) {
+                  TC* __restrict__ C, int ldc, int M, int N, int K, long long a_bs, long long w_bs,
+                  long long c_bs) {
+    // blockIdx.z is the member of a batch: its operands lie a_bs, w_bs, c_bs elements apart
+    A += (size_t)blockIdx.z * a_bs;
+    W += (size_t)blockIdx.z * w_bs;
+    C += (size_t)blockIdx.z * c_bs;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -73,10 +78,11 @@ gemm_plain_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, i
 
 template <typename TA, typename TW, typename TC>
 static int launch(const void* A, int lda, const void* W, int ldw, void* C, int ldc, int M, int N,
-                  int K, cudaStream_t s) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+                  int K, cudaStream_t s, int batch = 1, long long a_bs = 0, long long w_bs = 0,
+                  long long c_bs = 0) {
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     gemm_plain_kernel<TA, TW, TC><<<grid, 256, 0, s>>>((const TA*)A, lda, (const TW*)W, ldw,
-                                                        (TC*)C, ldc, M, N, K);
+                                                        (TC*)C, ldc, M, N, K, a_bs, w_bs, c_bs);
     IB_LAUNCH_CHECK();
     return IB_OK;
 }
@@ -97,6 +103,26 @@ IB_EXPORT int ib_gemm_plain(const void* A, int a_dtype, int lda, const void* W, 
         case 101: return launch<bf16, float, bf16>(A, lda, W, ldw, C, ldc, M, N, K, s);
         case 110: return launch<bf16, bf16, float>(A, lda, W, ldw, C, ldc, M, N, K, s);
         case 111: return launch<bf16, bf16, bf16>(A, lda, W, ldw, C, ldc, M, N, K, s);
+        default: return IB_ERR_UNSUPPORTED;
+    }
+}
+
+// A batch of such products, member b on A + b * a_bs, W + b * w_bs, C + b * c_bs
+// (strides in elements): one product per head, say, with the heads side by side
+// in the rows of A and C.  Same arithmetic, member by member.
+IB_EXPORT int ib_gemm_plain_batched(const void* A, int a_dtype, int lda, long long a_bs, const void* W,
+                                    int w_dtype, int ldw, long long w_bs, void* C, int c_dtype, int ldc,
+                                    long long c_bs, int batch, int M, int N, int K, void* stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return IB_OK;
+    if (!A || !W || !C || K <= 0 || lda < K || ldw < K || ldc < N) return IB_ERR_BAD_ARG;
+    if ((M + BM - 1) / BM > 65535 || batch > 65535) return IB_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int key = a_dtype * 100 + w_dtype * 10 + c_dtype;
+    switch (key) {
+        case 0: return launch<float, float, float>(A, lda, W, ldw, C, ldc, M, N, K, s, batch, a_bs, w_bs, c_bs);
+        case 10: return launch<float, bf16, float>(A, lda, W, ldw, C, ldc, M, N, K, s, batch, a_bs, w_bs, c_bs);
+        case 110: return launch<bf16, bf16, float>(A, lda, W, ldw, C, ldc, M, N, K, s, batch, a_bs, w_bs, c_bs);
+        case 111: return launch<bf16, bf16, bf16>(A, lda, W, ldw, C, ldc, M, N, K, s, batch, a_bs, w_bs, c_bs);
         default: return IB_ERR_UNSUPPORTED;
     }
 }

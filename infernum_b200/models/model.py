@@ -71,12 +71,17 @@ class Model:
         return all(part.all_replayable() for part in self._all_parts())
 
     def cache_needs(self) -> List[CacheNeed]:
+        """One need per schedule position and, when the embedding keeps state
+        of a request, one more behind them (``caches[len(schedule)]``)."""
         needs = []
         for pos, item in enumerate(self.schedule):
             mixer = self.layers[item.layer].mixer
             paged = mixer.cache_spec() if mixer is not None else None
             state = mixer.state_spec() if mixer is not None else None
             needs.append(CacheNeed(pos, paged, state, item.cache_of))
+        embed_state = self.embedding.state_spec() if hasattr(self.embedding, "state_spec") else None
+        if embed_state is not None:
+            needs.append(CacheNeed(len(self.schedule), None, embed_state, None))
         return needs
 
     def step_weight_bytes(self) -> int:
@@ -97,7 +102,11 @@ class Model:
         with core.step_stream(self.rt.device):
             # nothing of this step starts before what describes it (positions, tables) is complete
             core.step_fence(self.rt.device)
-            stream = ResidualStream(self.embedding.forward(ctx.token_ids))
+            if hasattr(self.embedding, "forward_step"):
+                embed_cache = caches[len(self.schedule)] if len(caches) > len(self.schedule) else None
+                stream = self.embedding.forward_step(ctx, embed_cache)
+            else:
+                stream = ResidualStream(self.embedding.forward(ctx.token_ids))
             for item, cache in zip(self.schedule, caches):
                 self.layers[item.layer].forward(stream, ctx, cache)
             if ctx.logit_rows is None or ctx.logit_rows.numel() == 0:

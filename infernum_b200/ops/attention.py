@@ -30,3 +30,15 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             return
     core.attention_plain(q, k_pool, v_pool, out, ctx.positions, ctx.row_entry, tables, n_heads,
                          scale, window, rt.err)
+
+
+def latent_attention(q_abs: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, kv_rank: int, ctx,
+                     tables: torch.Tensor, scale: float, window: int, rt) -> None:
+    """Attention of every head of every row over its request's cached latents.
+
+    ``q_abs`` [N, heads, kv_rank + rot_dim] holds each head's query in latent
+    space followed by its rotated part; the pool [pages, 1, page_size,
+    kv_rank + rot_dim] each token's latent followed by the shared rotated key;
+    ``out`` [N, heads, kv_rank] receives the weighted sums of latents."""
+    core.attention_latent_plain(q_abs, pool, out, kv_rank, ctx.positions, ctx.row_entry, tables, scale,
+                                window, rt.err)

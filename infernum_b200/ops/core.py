@@ -16,7 +16,8 @@ import torch
 from ..csrc.build import load_module
 from ..errors import KernelError
 
-CORE_SOURCES = ["elementwise.cu", "attention_plain.cu", "gemm_plain.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "attention_plain.cu", "gemm_plain.cu", "sampling.cu", "layernorm.cu",
+                "embed_hashed.cu", "latent.cu", "moe.cu"]
 
 _c_int = ctypes.c_int
 _c_float = ctypes.c_float
@@ -80,6 +81,29 @@ def core_lib() -> ctypes.CDLL:
                                           _c_void_p]
         lib.ib_feed_tokens.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p,
                                        _c_void_p]
+        lib.ib_attention_plain_ex.argtypes = lib.ib_attention_plain.argtypes[:19] + [_c_int, _c_int, _c_int, _c_int,
+                                                                                  _c_void_p, _c_void_p]
+        lib.ib_gemm_plain_batched.argtypes = [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_ll,
+                                              _c_void_p, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int,
+                                              _c_void_p]
+        lib.ib_gated_act.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int,
+                                     _c_void_p]
+        lib.ib_scale_add_norm.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
+                                          _c_void_p, _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_void_p]
+        lib.ib_softcap.argtypes = [_c_void_p, _c_ll, _c_float, _c_void_p]
+        lib.ib_embed_hashed.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                        _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                                        _c_ll, _c_ll, _c_ll, _c_void_p, _c_void_p]
+        lib.ib_latent_prepare.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                                          _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                                          _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
+        lib.ib_latent_q_rotate.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                                           _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_moe_route.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                     _c_int, _c_void_p]
+        for fn in ("ib_attention_plain_ex", "ib_gemm_plain_batched", "ib_gated_act", "ib_scale_add_norm",
+                   "ib_softcap", "ib_embed_hashed", "ib_latent_prepare", "ib_latent_q_rotate", "ib_moe_route"):
+            getattr(lib, fn).restype = _c_int
         for fn in ("ib_decode_advance", "ib_feed_tokens", "ib_embed", "ib_add_rmsnorm", "ib_residual_add", "ib_rope_append",
                    "ib_silu_mul", "ib_attention_plain", "ib_gemm_plain", "ib_argmax", "ib_sample"):
             getattr(lib, fn).restype = _c_int
@@ -492,3 +516,217 @@ def decode_advance(tokens: torch.Tensor, selected: Optional[torch.Tensor], posit
                                        kv_len.data_ptr(), _ptr(slot_ids), int(pad_slot), tokens.numel(),
                                        stream_ptr(tokens)),
           "decode_advance")
+
+
+# ---------------------------------------------------------------------------
+# Parts that several designs share beyond the Llama decoder: a norm of a scaled
+# sum (post-norm layers, layer norm with bias), gated activations other than
+# SiLU, a soft cap on logits, a hashed bigram embedding, attention over a latent
+# cache, batched per-head products, and the routing of a mixture of experts.
+# ---------------------------------------------------------------------------
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def scale_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                   bias: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor], alpha: float = 1.0,
+                   centred: bool = True, store: bool = False, row_idx: Optional[torch.Tensor] = None) -> None:
+    """y = norm(alpha * residual + delta) * weight + bias in 32-bit; ``centred``
+    takes the mean off first (layer norm), else it is an RMS norm.  ``store``
+    writes y over the float32 residual; ``out`` receives it in the activation
+    dtype (compact when ``row_idx`` selects rows)."""
+    require_cuda(residual, delta, weight, bias, out, row_idx)
+    N, H = residual.shape
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise KernelError("scale_add_norm: residual must be contiguous float32")
+    _int32(row_idx, "row_idx")
+    n_out = N if row_idx is None else row_idx.numel()
+    if out is not None and (out.shape != (n_out, H) or not out.is_contiguous()):
+        raise KernelError(f"scale_add_norm: out must be contiguous [{n_out}, {H}]")
+    if out is None and not store:
+        raise KernelError("scale_add_norm: nothing to write")
+    act = out.dtype if out is not None else (delta.dtype if delta is not None else torch.float32)
+    if delta is not None and (delta.shape != residual.shape or delta.dtype != act or not delta.is_contiguous()):
+        raise KernelError("scale_add_norm: delta must match the residual's shape and the activation dtype")
+    if weight.shape != (H,) or not weight.is_contiguous() or (
+            bias is not None and (bias.shape != (H,) or bias.dtype != weight.dtype or not bias.is_contiguous())):
+        raise KernelError(f"scale_add_norm: weight and bias must be [{H}] of one dtype")
+    check(core_lib().ib_scale_add_norm(residual.data_ptr(), _ptr(delta), weight.data_ptr(), _ptr(bias),
+                                       dtype_code(weight.dtype), _ptr(out), dtype_code(act), _ptr(row_idx), n_out,
+                                       H, float(eps), float(alpha), 1 if centred else 0, 1 if store else 0,
+                                       stream_ptr(residual)), "scale_add_norm")
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), in place (float32)."""
+    require_cuda(logits)
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise KernelError("softcap: logits must be contiguous float32")
+    check(core_lib().ib_softcap(logits.data_ptr(), logits.numel(), float(cap), stream_ptr(logits)), "softcap")
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", block: Optional[int] = None,
+              scale: Optional[torch.Tensor] = None, cols_per_scale: int = 0) -> None:
+    """out = act(gate) * up for rows [N, 2I] (``block`` as in ``silu_mul``); with
+    ``scale`` [N, I / cols_per_scale] (float32) each run of ``cols_per_scale``
+    outputs is multiplied by its scale."""
+    require_cuda(gate_up, out, scale)
+    N, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (N, two_i // 2) or out.dtype != gate_up.dtype \
+            or not gate_up.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gated_act: gate_up [N, 2I] and out [N, I] must be contiguous, same dtype")
+    I = two_i // 2
+    blk = I if block is None else int(block)
+    if blk <= 0 or I % blk:
+        raise KernelError(f"gated_act: block {blk} does not divide the width {I}")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gated_act: unknown activation {activation!r}; known: {sorted(ACTIVATIONS)}")
+    if scale is not None and (scale.dtype != torch.float32 or not scale.is_contiguous() or cols_per_scale <= 0
+                              or I % cols_per_scale or scale.shape != (N, I // cols_per_scale)):
+        raise KernelError("gated_act: scale must be contiguous float32 [N, I / cols_per_scale]")
+    check(core_lib().ib_gated_act(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), N, I, blk,
+                                  ACTIVATIONS[activation], _ptr(scale), int(cols_per_scale), stream_ptr(out)),
+          "gated_act")
+
+
+def embed_hashed(ctx, prev_state: torch.Tensor, table: torch.Tensor, bigram: torch.Tensor, buckets: int,
+                 mul_prev: int, mul_cur: int, out: torch.Tensor, out_act: Optional[torch.Tensor],
+                 err: torch.Tensor) -> None:
+    """out[t] = table[id_t] + bigram[hash(id_{t-1}, id_t)] (row ``buckets`` for a
+    sequence's first token); ``prev_state`` [slots] int32 carries each request's
+    last token from step to step."""
+    ids = ctx.token_ids
+    require_cuda(ids, prev_state, table, bigram, out, out_act, err)
+    _int32(ids, "ids")
+    _int32(prev_state, "prev_state")
+    n = ids.numel()
+    V, H = table.shape
+    if bigram.shape != (buckets + 1, H) or bigram.dtype != table.dtype or not bigram.is_contiguous() \
+            or not table.is_contiguous():
+        raise KernelError(f"embed_hashed: the bigram table must be [{buckets + 1}, {H}] of the table's dtype")
+    if out.dtype != torch.float32 or out.shape != (n, H) or not out.is_contiguous():
+        raise KernelError(f"embed_hashed: out must be contiguous float32 [{n}, {H}]")
+    if out_act is not None and (out_act.dtype != torch.bfloat16 or out_act.shape != (n, H)
+                                or not out_act.is_contiguous()):
+        raise KernelError("embed_hashed: the activation copy must be contiguous bfloat16")
+    check(core_lib().ib_embed_hashed(ids.data_ptr(), ctx.positions.data_ptr(), ctx.row_entry.data_ptr(),
+                                     ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(), prev_state.data_ptr(),
+                                     prev_state.numel(), table.data_ptr(), bigram.data_ptr(),
+                                     dtype_code(table.dtype), out.data_ptr(), _ptr(out_act), n, H, V, int(buckets),
+                                     int(mul_prev), int(mul_cur), err.data_ptr(), stream_ptr(out)), "embed_hashed")
+
+
+def latent_prepare(lat: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, rotary_dim: int,
+                   wq: Optional[torch.Tensor], wkv: Optional[torch.Tensor], eps: float,
+                   inv_freq: Optional[torch.Tensor], positions: torch.Tensor, row_entry: torch.Tensor,
+                   block_tables: Optional[torch.Tensor], cq_out: Optional[torch.Tensor],
+                   pool: Optional[torch.Tensor], err: torch.Tensor) -> None:
+    """From the down projections ``lat`` [N, q_rank + kv_rank + rot_dim] (float32):
+    the normed query latent into ``cq_out``, and - with ``pool`` - the normed
+    key/value latent and the rotated shared key part into the token's place in
+    the pool [pages, 1, page_size, kv_rank + rot_dim]."""
+    require_cuda(lat, wq, wkv, inv_freq, positions, row_entry, block_tables, cq_out, pool, err)
+    _int32(positions, "positions")
+    _int32(row_entry, "row_entry")
+    _int32(block_tables, "block_tables")
+    write_kv = pool is not None
+    if lat.dtype != torch.float32 or lat.dim() != 2 or lat.stride(1) != 1:
+        raise KernelError("latent_prepare: the down projections must be float32 rows")
+    act = cq_out.dtype if cq_out is not None else pool.dtype
+    for t, n, name in ((wq, q_rank, "query"), (wkv if write_kv else None, kv_rank, "key/value")):
+        if t is not None and (t.shape != (n,) or t.dtype != act or not t.is_contiguous()):
+            raise KernelError(f"latent_prepare: the {name} norm weight must be [{n}] in the activation dtype")
+    if q_rank and (cq_out is None or cq_out.shape != (lat.shape[0], q_rank) or not cq_out.is_contiguous()):
+        raise KernelError("latent_prepare: cq_out must be contiguous [N, q_rank]")
+    page_size = num_pages = max_blocks = 0
+    if write_kv:
+        if pool.dim() != 4 or pool.shape[1] != 1 or pool.shape[3] != kv_rank + rot_dim or pool.dtype != act \
+                or not pool.is_contiguous():
+            raise KernelError("latent_prepare: the pool must be contiguous [pages, 1, page_size, kv_rank + rot_dim]")
+        num_pages, _, page_size, _ = pool.shape
+        max_blocks = block_tables.shape[1]
+        if rotary_dim and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
+            raise KernelError("latent_prepare: inv_freq must be float32 [rotary_dim / 2]")
+    check(core_lib().ib_latent_prepare(lat.data_ptr(), lat.stride(0), int(q_rank), int(kv_rank), int(rot_dim),
+                                       int(rotary_dim), _ptr(wq), _ptr(wkv), float(eps), _ptr(inv_freq),
+                                       positions.data_ptr(), row_entry.data_ptr(), _ptr(block_tables), max_blocks,
+                                       _ptr(cq_out), _ptr(pool), dtype_code(act), page_size, num_pages,
+                                       1 if write_kv else 0, lat.shape[0], err.data_ptr(), stream_ptr(lat)),
+          "latent_prepare")
+
+
+def latent_q_rotate(q: torch.Tensor, heads: int, dim: int, rot_dim: int, rotary_dim: int,
+                    inv_freq: Optional[torch.Tensor], positions: torch.Tensor, q_abs: torch.Tensor,
+                    offset: int) -> None:
+    """The rotated part of each head of ``q`` [N, heads * (dim + rot_dim)], rotated
+    by its row's position, into ``q_abs[N, heads, offset : offset + rot_dim]``."""
+    require_cuda(q, inv_freq, positions, q_abs)
+    _int32(positions, "positions")
+    if q.dim() != 2 or q.stride(1) != 1 or q_abs.dim() != 3 or q_abs.stride(2) != 1 or q_abs.dtype != q.dtype \
+            or q_abs.shape[0] != q.shape[0] or q_abs.shape[1] != heads or q_abs.shape[2] < offset + rot_dim:
+        raise KernelError("latent_q_rotate: q [N, heads*(dim+rot)] and q_abs [N, heads, >= offset+rot] do not fit")
+    check(core_lib().ib_latent_q_rotate(q.data_ptr(), q.stride(0), int(heads), int(dim), int(rot_dim),
+                                        int(rotary_dim), _ptr(inv_freq), positions.data_ptr(), q_abs.data_ptr(),
+                                        q_abs.stride(0), q_abs.stride(1), int(offset), dtype_code(q.dtype),
+                                        q.shape[0], stream_ptr(q)), "latent_q_rotate")
+
+
+def attention_latent_plain(q_abs: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, kv_rank: int,
+                           positions: torch.Tensor, row_entry: torch.Tensor, block_tables: torch.Tensor,
+                           scale: float, window: int, err: torch.Tensor) -> None:
+    """Attention of all heads over one latent cache, in 32-bit: ``q_abs``
+    [N, heads, width] holds each head's query in latent space followed by its
+    rotated part, the pool [pages, 1, page_size, width] each token's latent
+    followed by the shared rotated key; a token's value is its latent.  ``out``
+    [N, heads, kv_rank]."""
+    require_cuda(q_abs, pool, out, positions, row_entry, block_tables, err)
+    _int32(positions, "positions")
+    _int32(row_entry, "row_entry")
+    _int32(block_tables, "block_tables")
+    num_pages, one, page_size, width = pool.shape
+    N, heads, qw = q_abs.shape
+    if one != 1 or qw != width or q_abs.stride(2) != 1 or out.stride(2) != 1 or out.shape != (N, heads, kv_rank) \
+            or not (q_abs.dtype == pool.dtype == out.dtype) or not pool.is_contiguous() \
+            or q_abs.stride(1) * heads > q_abs.stride(0) or out.stride(1) * heads > out.stride(0):
+        raise KernelError("attention_latent_plain: q_abs [N, heads, width], pool [pages, 1, page, width] and "
+                          "out [N, heads, kv_rank] do not fit")
+    check(core_lib().ib_attention_plain_ex(q_abs.data_ptr(), q_abs.stride(0), pool.data_ptr(), pool.data_ptr(),
+                                           out.data_ptr(), out.stride(0), dtype_code(q_abs.dtype),
+                                           positions.data_ptr(), row_entry.data_ptr(), block_tables.data_ptr(),
+                                           block_tables.shape[1], N, heads, 1, width, page_size, num_pages,
+                                           int(window), float(scale), int(kv_rank), width, q_abs.stride(1),
+                                           out.stride(1), err.data_ptr(), stream_ptr(q_abs)),
+          "attention_latent_plain")
+
+
+def gemm_plain_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b, M, N] = a[b, M, K] @ w[b, N, K]^T member by member with the plain
+    kernel's arithmetic.  Any batch and row strides (views of heads that lie
+    side by side in a row are fine); inner strides 1."""
+    require_cuda(a, w, out)
+    B, M, K = a.shape
+    if w.dim() != 3 or w.shape[0] != B or w.shape[2] != K or out.shape != (B, M, w.shape[1]):
+        raise KernelError(f"gemm_plain_batched: shapes {tuple(a.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    if a.stride(2) != 1 or w.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError("gemm_plain_batched: inner strides must be 1")
+    check(core_lib().ib_gemm_plain_batched(a.data_ptr(), dtype_code(a.dtype), a.stride(1), a.stride(0),
+                                           w.data_ptr(), dtype_code(w.dtype), w.stride(1), w.stride(0),
+                                           out.data_ptr(), dtype_code(out.dtype), out.stride(1), out.stride(0),
+                                           B, M, w.shape[1], K, stream_ptr(out)), "gemm_plain_batched")
+
+
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor,
+              weights: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+    """The ``top`` largest of ``logits + bias`` per row (float32) with the softmax
+    over those: ``ids`` / ``weights`` [N, top], and ``gate`` [N, E] dense."""
+    require_cuda(logits, bias, ids, weights, gate)
+    _int32(ids, "ids")
+    N, E = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or ids.shape != (N, top) \
+            or weights.shape != (N, top) or weights.dtype != torch.float32 or not weights.is_contiguous():
+        raise KernelError("moe_route: logits float32 [N, E], ids int32 [N, top], weights float32 [N, top]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (E,) or not bias.is_contiguous()):
+        raise KernelError("moe_route: the bias must be float32 [E]")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (N, E) or not gate.is_contiguous()):
+        raise KernelError("moe_route: gate must be contiguous float32 [N, E]")
+    check(core_lib().ib_moe_route(logits.data_ptr(), logits.stride(0), _ptr(bias), E, int(top), ids.data_ptr(),
+                                  weights.data_ptr(), _ptr(gate), N, stream_ptr(logits)), "moe_route")

@@ -222,13 +222,13 @@ def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: Optional[tor
 
 
 def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
-                 err: Optional[torch.Tensor] = None) -> bool:
+                 err: Optional[torch.Tensor] = None, activation: str = "silu") -> bool:
     """The gate/up product with SiLU(gate) * up applied in its epilogue, when
     the policy and the operands allow; ``out`` is [T, I].  Up to 64 tokens go to
     the kernel that streams the weights once (decode), prompts to the kernel on
     pairs of SMs when their length suits its tiles (``pair_suits``)."""
     mode = POLICY["mode"]
-    if mode in ("none", "cublas", "library"):
+    if mode in ("none", "cublas", "library") or activation != "silu":
         return False
     if w_interleaved.shape[0] % 128 or out.dtype != torch.bfloat16:
         return False

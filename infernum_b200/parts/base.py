@@ -44,6 +44,9 @@ class WeightSpec:
     std: float = 0.02
     # another tensor name to take when this one is absent from the checkpoint
     fallback: Optional[str] = None
+    # True: the checkpoint may leave the tensor out; the part is then bound without
+    # it and must cope (the random-weights mode always draws it)
+    optional: bool = False
 
 
 @dataclass(frozen=True)
@@ -59,6 +62,8 @@ class LayerSpec:
     block: str
     parts: Dict[str, PartSpec]
     name: str = ""
+    # the block arrangement's own constants (a residual scale, say)
+    params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -90,11 +95,23 @@ class ModelSpec:
 class PagedCacheSpec:
     """What a mixer needs from the paged cache: keys and values of
     ``kv_heads`` x ``head_dim`` per token; ``window`` > 0 means only the last
-    ``window`` tokens are ever read, so older pages can be given back."""
+    ``window`` tokens are ever read, so older pages can be given back.
+    ``v_head_dim``: the size of a value when it differs from a key's; 0 means
+    the mixer keeps no values of their own (a latent cache, where keys and
+    values are made from the one cached vector): only the key pool exists."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else int(self.v_head_dim)
+
+    def elements_per_token(self) -> int:
+        """Cached values per token and member layer."""
+        return self.kv_heads * (self.head_dim + self.value_dim)
 
 
 @dataclass(frozen=True)
@@ -183,6 +200,23 @@ class PositionEncoding(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """From token ids to the float32 residual stream.  ``forward_step(ctx,
+    cache)`` returns the ``ResidualStream`` of the step's rows; an embedding
+    that needs something of the request besides the step's tokens (the token
+    before a portion, say) declares it with ``state_spec()`` and finds it in
+    ``cache.state[slot]``."""
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def forward_step(self, ctx: Any, cache: Any) -> "ResidualStream":
+        return ResidualStream(self.forward(ctx.token_ids))
+
+
 class Mixer(Part):
     """Token mixing (attention, or anything that moves information between
     positions).  ``forward(x, ctx, cache)``: ``x`` is [N, hidden] in the
@@ -244,9 +278,13 @@ class ResidualStream:
     ``flush``) adds to it.  Keeping the sum in 32-bit and fusing the add into
     the norm kernel saves one pass over the rows per sub-layer."""
 
-    def __init__(self, residual: torch.Tensor):
+    def __init__(self, residual: torch.Tensor, act: Optional[torch.Tensor] = None):
         self.residual = residual
         self.pending: Optional[torch.Tensor] = None
+        # The residual rounded to the activation dtype, for arrangements whose
+        # sub-layers read the stream itself (norm after the sum); valid while
+        # nothing is pending.  In a float32 engine it is the residual.
+        self.act = act
 
     def push(self, delta: torch.Tensor) -> None:
         if self.pending is not None:
@@ -323,7 +361,7 @@ def build_part(role: str, spec: PartSpec, rt: Runtime) -> Part:
 
 def build_layer(spec: LayerSpec, rt: Runtime) -> Block:
     parts = {role: build_part(role, ps, rt) for role, ps in spec.parts.items()}
-    return BLOCKS.get(spec.block)({"name": spec.name}, rt, parts)
+    return BLOCKS.get(spec.block)({**spec.params, "name": spec.name}, rt, parts)
 
 
 def register_mixer(kind: str, factory=None):

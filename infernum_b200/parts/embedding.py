@@ -18,12 +18,12 @@ from typing import Dict, Optional
 import torch
 
 from ..ops import core
-from .base import EMBEDDINGS, HEADS, Part, Runtime, WeightSpec
+from .base import EMBEDDINGS, HEADS, Embedding, Part, ResidualStream, Runtime, StateSpec, WeightSpec
 from .linear import Linear
 
 
 @EMBEDDINGS.register("token_embedding")
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     def __init__(self, params, rt: Runtime):
         super().__init__(params, rt)
         self.vocab_size = int(params["vocab_size"])
@@ -44,6 +44,52 @@ class TokenEmbedding(Part):
         return out
 
 
+@EMBEDDINGS.register("hashed_bigram_embedding")
+class HashedBigramEmbedding(Embedding):
+    """``h[t] = E[id_t] + B[(id_{t-1} * mul_prev + id_t * mul_cur) mod buckets]``;
+    a sequence's first token takes the extra last row of ``B`` ([buckets + 1,
+    hidden]).  The token before a portion's first is the request's state (one
+    int32 per request slot), so that a prompt may be cut anywhere and a decoded
+    token finds its predecessor on the device.  The stream gets the float32 sum
+    and its rounding to the activation dtype.
+
+    Parameters: ``vocab_size``, ``hidden_size``, ``weight``, ``bigram_weight``,
+    ``buckets``, ``mul_prev``, ``mul_cur``.
+    """
+
+    def __init__(self, params, rt: Runtime):
+        super().__init__(params, rt)
+        self.vocab_size = int(params["vocab_size"])
+        self.hidden_size = int(params["hidden_size"])
+        self.weight_name = params["weight"]
+        self.bigram_name = params["bigram_weight"]
+        self.buckets = int(params["buckets"])
+        self.mul_prev = int(params["mul_prev"])
+        self.mul_cur = int(params["mul_cur"])
+        self.weight: Optional[torch.Tensor] = None
+        self.bigram: Optional[torch.Tensor] = None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return StateSpec((1,), torch.int32)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.vocab_size, self.hidden_size)),
+                self.bigram_name: WeightSpec((self.buckets + 1, self.hidden_size))}
+
+    def bind(self, weights) -> None:
+        self.weight = weights[self.weight_name].contiguous()
+        self.bigram = weights[self.bigram_name].to(self.weight.dtype).contiguous()
+
+    def forward_step(self, ctx, cache) -> ResidualStream:
+        n = ctx.token_ids.numel()
+        dev = ctx.token_ids.device
+        out = torch.empty((n, self.hidden_size), dtype=torch.float32, device=dev)
+        act = None if self.rt.is_fp32 else torch.empty((n, self.hidden_size), dtype=self.rt.dtype, device=dev)
+        core.embed_hashed(ctx, cache.state.view(-1), self.weight, self.bigram, self.buckets, self.mul_prev,
+                          self.mul_cur, out, act, self.rt.err)
+        return ResidualStream(out, out if act is None else act)
+
+
 @HEADS.register("linear_head")
 class LinearHead(Part):
     def __init__(self, params, rt: Runtime):
@@ -53,6 +99,8 @@ class LinearHead(Part):
         self.weight_name = params["weight"]
         self.tied_to = params.get("tied_to")
         self.fallback = params.get("fallback")
+        # logits <- softcap * tanh(logits / softcap) when given
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
         self.proj: Optional[Linear] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -68,4 +116,7 @@ class LinearHead(Part):
         return self.proj.nbytes
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.proj(x, out_dtype=torch.float32)
+        logits = self.proj(x, out_dtype=torch.float32)
+        if self.softcap is not None:
+            core.softcap(logits, self.softcap)
+        return logits

@@ -60,6 +60,15 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
     return out
 
 
+def batched_matmul_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[b] = x[b] @ w[b]^T`` for ``x`` [B, M, K], ``w`` [B, N, K], ``out``
+    [B, M, N]; any batch and row strides (the members may be heads lying side by
+    side in the rows of one matrix), inner strides 1.  The package's plain
+    kernel: 32-bit multiply-adds in k order for every dtype."""
+    core.gemm_plain_batched(x, w, out)
+    return out
+
+
 class Linear:
     """A weight and its product; ``parts`` own these, they are not parts."""
 

@@ -9,7 +9,10 @@ otherwise it is the plain concatenation ``[Wg; Wu]``.  Only the fused copy is
 kept.
 
 Parameters: ``hidden_size``, ``intermediate_size``, ``prefix`` (checkpoint
-prefix, e.g. "model.layers.0.mlp.").
+prefix, e.g. "model.layers.0.mlp."), ``names`` (the three tensors' names
+behind the prefix, default gate_proj.weight / up_proj.weight /
+down_proj.weight), ``activation`` of the gate: "silu" (default) or
+"gelu_tanh", ``0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))``.
 """
 
 from __future__ import annotations
@@ -31,20 +34,26 @@ class SwiGLU(FeedForward):
         self.hidden_size = int(params["hidden_size"])
         self.intermediate_size = int(params["intermediate_size"])
         self.prefix = params.get("prefix", "")
+        names = params.get("names") or {}
+        self.names = {k: self.prefix + names.get(k, f"{k}_proj.weight") for k in ("gate", "up", "down")}
+        self.activation = params.get("activation", "silu")
+        if self.activation not in core.ACTIVATIONS:
+            raise ConfigError(f"gated feed-forward: unknown activation {self.activation!r}; "
+                              f"known: {sorted(core.ACTIVATIONS)}")
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h, i = self.hidden_size, self.intermediate_size
         return {
-            self.prefix + "gate_proj.weight": WeightSpec((i, h)),
-            self.prefix + "up_proj.weight": WeightSpec((i, h)),
-            self.prefix + "down_proj.weight": WeightSpec((h, i)),
+            self.names["gate"]: WeightSpec((i, h)),
+            self.names["up"]: WeightSpec((i, h)),
+            self.names["down"]: WeightSpec((h, i)),
         }
 
     def bind(self, weights) -> None:
-        gate = weights[self.prefix + "gate_proj.weight"]
-        up = weights[self.prefix + "up_proj.weight"]
+        gate = weights[self.names["gate"]]
+        up = weights[self.names["up"]]
         if gate.dtype != up.dtype:
             raise ConfigError(f"{self.prefix}: gate and up projections are stored in different dtypes")
         i, h = self.intermediate_size, self.hidden_size
@@ -55,7 +64,7 @@ class SwiGLU(FeedForward):
             self.block = 64
         else:
             self.gate_up = Linear(torch.cat([gate, up], dim=0), self.rt)
-        self.down = Linear(weights[self.prefix + "down_proj.weight"], self.rt)
+        self.down = Linear(weights[self.names["down"]], self.rt)
 
     def weight_bytes(self) -> int:
         return self.gate_up.nbytes + self.down.nbytes
@@ -66,7 +75,8 @@ class SwiGLU(FeedForward):
         if self.block == 64 and x.dtype == torch.bfloat16 and self.gate_up.weight.dtype == torch.bfloat16:
             from ..ops import gemm_tc
 
-            fused = gemm_tc.swiglu_route(x, self.gate_up.weight, act, self.gate_up.err)
+            fused = gemm_tc.swiglu_route(x, self.gate_up.weight, act, self.gate_up.err,
+                                         activation=self.activation)
         if not fused:
-            core.silu_mul(self.gate_up(x), act, block=self.block)
+            core.gated_act(self.gate_up(x), act, self.activation, block=self.block)
         return self.down(act)

@@ -1,0 +1,115 @@
+"""Mixture of experts: ``experts`` small gated feed-forwards without biases, of
+which each token uses the ``top`` with the largest router logits,
+``z = W_r x + b_r`` in 32-bit; the chosen experts' weights are the softmax over
+the chosen logits only, and the output is the weighted sum of their outputs,
+``sum_k w_k Wd_k (act(Wg_k x) * (Wu_k x))``.
+
+How it runs: routing stays on the device (``moe_route``: ids and weights per
+token, and the dense row ``gate[N, experts]`` that is 0 for experts not chosen),
+so a recorded step replays.  The experts' gate/up weights are kept as one
+stacked matrix ``[experts * 2 ff, hidden]`` and their down weights side by side
+as ``[hidden, experts * ff]``; one product gives every expert's gate and up
+values, the activation kernel multiplies each expert's run of ``ff`` outputs by
+the token's weight for that expert (0 where it was not chosen), and the down
+product sums over all experts at once: ``sum_e Wd_e (w_e a_e)`` is one product
+with the concatenated vector.  Every expert is computed for every token; what
+a token did not choose is multiplied by an exact 0.
+
+Parameters: ``hidden_size``, ``expert_size`` (ff), ``experts``, ``top``,
+``activation`` ("silu" | "gelu_tanh"), ``prefix``, ``expert_names`` (format of
+an expert's tensors behind the prefix, default "e{e}.{w}" with w in gate, up,
+down), ``router`` and ``router_bias`` (names behind the prefix; bias None for
+none).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..errors import ConfigError
+from ..ops import core
+from .base import FEED_FORWARDS, FeedForward, Runtime, WeightSpec
+from .linear import Linear
+
+
+@FEED_FORWARDS.register("moe")
+class MixtureOfExperts(FeedForward):
+    def __init__(self, params, rt: Runtime):
+        super().__init__(params, rt)
+        self.hidden_size = int(params["hidden_size"])
+        self.expert_size = int(params["expert_size"])
+        self.experts = int(params["experts"])
+        self.top = int(params["top"])
+        if not 0 < self.top <= self.experts:
+            raise ConfigError(f"mixture of experts: top {self.top} must be within 1..{self.experts}")
+        self.activation = params.get("activation", "silu")
+        if self.activation not in core.ACTIVATIONS:
+            raise ConfigError(f"mixture of experts: unknown activation {self.activation!r}")
+        self.prefix = params.get("prefix", "")
+        self.expert_names = params.get("expert_names", "e{e}.{w}")
+        self.router_name = self.prefix + params.get("router", "router")
+        bias = params.get("router_bias", "router.b")
+        self.bias_name = self.prefix + bias if bias else None
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+        self.router: Optional[torch.Tensor] = None
+        self.router_bias: Optional[torch.Tensor] = None
+
+    def _name(self, e: int, w: str) -> str:
+        return self.prefix + self.expert_names.format(e=e, w=w)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        h, f = self.hidden_size, self.expert_size
+        specs = {self.router_name: WeightSpec((self.experts, h), std=0.5)}
+        if self.bias_name:
+            specs[self.bias_name] = WeightSpec((self.experts,), std=0.5)
+        for e in range(self.experts):
+            specs[self._name(e, "gate")] = WeightSpec((f, h))
+            specs[self._name(e, "up")] = WeightSpec((f, h))
+            specs[self._name(e, "down")] = WeightSpec((h, f))
+        return specs
+
+    def bind(self, weights) -> None:
+        E, f, h = self.experts, self.expert_size, self.hidden_size
+        gates = [weights[self._name(e, "gate")] for e in range(E)]
+        ups = [weights[self._name(e, "up")] for e in range(E)]
+        downs = [weights[self._name(e, "down")] for e in range(E)]
+        if len({t.dtype for t in gates + ups + downs}) != 1:
+            raise ConfigError(f"{self.prefix}: the experts are stored in different dtypes")
+        # one gated feed-forward of width E * ff: expert e owns outputs [e ff, (e + 1) ff)
+        gate, up = torch.cat(gates, dim=0), torch.cat(ups, dim=0)
+        I = E * f
+        self.block = None
+        if I % 64 == 0:
+            fused = torch.stack([gate.view(I // 64, 64, h), up.view(I // 64, 64, h)], dim=1).reshape(2 * I, h)
+            self.block = 64
+        else:
+            fused = torch.cat([gate, up], dim=0)
+        self.gate_up = Linear(fused, self.rt)
+        self.down = Linear(torch.cat(downs, dim=1), self.rt)
+        # the router is 32-bit arithmetic whatever the engine's dtype
+        self.router = weights[self.router_name].contiguous()
+        self.router_bias = weights[self.bias_name].to(torch.float32).contiguous() if self.bias_name else None
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.nbytes + self.down.nbytes + self.router.numel() * self.router.element_size()
+
+    def route(self, x: torch.Tensor):
+        """(ids [N, top] int32, weights [N, top] float32, gate [N, experts] float32)."""
+        n, dev = x.shape[0], x.device
+        logits = torch.empty((n, self.experts), dtype=torch.float32, device=dev)
+        core.gemm_plain(x, self.router, logits)  # 32-bit multiply-adds in k order
+        ids = torch.empty((n, self.top), dtype=torch.int32, device=dev)
+        wts = torch.empty((n, self.top), dtype=torch.float32, device=dev)
+        gate = torch.empty((n, self.experts), dtype=torch.float32, device=dev)
+        core.moe_route(logits, self.router_bias, self.top, ids, wts, gate)
+        return ids, wts, gate
+
+    def forward(self, x: torch.Tensor, ctx=None) -> torch.Tensor:
+        _ids, _wts, gate = self.route(x)
+        act = torch.empty((x.shape[0], self.experts * self.expert_size), dtype=x.dtype, device=x.device)
+        core.gated_act(self.gate_up(x), act, self.activation, block=self.block, scale=gate,
+                       cols_per_scale=self.expert_size)
+        return self.down(act)

@@ -48,3 +48,75 @@ class RMSNorm(Norm):
         out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
         core.add_rmsnorm(x, None, self.weight, self.eps, out)
         return out
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """Layer norm with weight and optional bias, or - ``centred: False`` - an RMS
+    norm through the same kernel: ``y = (s - mean(s)) / sqrt(var(s) + eps) * w + b``
+    with ``var`` the mean of the squared deviations, all in 32-bit.
+
+    Two uses.  ``forward(stream, row_idx)`` is the pre-norm / final-norm use:
+    the stream's pending delta is folded into the residual and the normed rows
+    are returned.  ``renorm(stream, alpha)`` is the use of layers that norm
+    after the sum: the residual becomes ``norm(alpha * residual + pending)``
+    (kept in float32) and ``stream.act`` its rounding to the activation dtype.
+
+    Parameters: ``hidden_size``, ``eps``, ``weight``, ``bias`` (tensor name or
+    None), ``centred`` (default True).
+    """
+
+    def __init__(self, params, rt: Runtime):
+        super().__init__(params, rt)
+        self.hidden_size = int(params["hidden_size"])
+        self.eps = float(params["eps"])
+        self.weight_name = params["weight"]
+        self.bias_name = params.get("bias")
+        self.centred = bool(params.get("centred", True))
+        self.optional = bool(params.get("optional", False))
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = {self.weight_name: WeightSpec((self.hidden_size,), init="norm", optional=self.optional)}
+        if self.bias_name:
+            specs[self.bias_name] = WeightSpec((self.hidden_size,), init="normal", std=0.05,
+                                               optional=self.optional)
+        return specs
+
+    def bind(self, weights) -> None:
+        w = weights.get(self.weight_name)
+        self.weight = w.contiguous() if w is not None else None
+        b = weights.get(self.bias_name) if self.bias_name else None
+        self.bias = b.contiguous() if b is not None else None
+
+    @property
+    def present(self) -> bool:
+        """False for an optional norm whose tensors the checkpoint left out."""
+        return self.weight is not None
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.weight, self.bias) if t is not None)
+
+    def forward(self, stream: ResidualStream, row_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if stream.pending is not None:
+            stream.flush()
+        residual = stream.residual
+        n_out = residual.shape[0] if row_idx is None else row_idx.numel()
+        out = torch.empty((n_out, self.hidden_size), dtype=self.rt.dtype, device=residual.device)
+        core.scale_add_norm(residual, None, self.weight, self.bias, self.eps, out, alpha=1.0,
+                            centred=self.centred, store=False, row_idx=row_idx)
+        return out
+
+    def renorm(self, stream: ResidualStream, alpha: float) -> None:
+        residual = stream.residual
+        out = None if self.rt.is_fp32 else torch.empty(residual.shape, dtype=self.rt.dtype, device=residual.device)
+        core.scale_add_norm(residual, stream.pending, self.weight, self.bias, self.eps, out, alpha=alpha,
+                            centred=self.centred, store=True)
+        stream.pending = None
+        stream.act = residual if out is None else out
+
+    def apply(self, x: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        core.scale_add_norm(x, None, self.weight, self.bias, self.eps, out, centred=self.centred)
+        return out

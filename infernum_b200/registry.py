@@ -50,9 +50,10 @@ def resolve(name: str) -> Architecture:
 
 
 def resolve_config(config: Mapping[str, Any]):
-    """(architecture, typed config) for a config.json dict; a missing
-    ``model_type`` means "llama" as in the reference (config.rs:21-22)."""
-    arch = resolve(config.get("model_type", "llama"))
+    """(architecture, typed config) for a config.json dict.  The name is the
+    value of ``model_type`` or, for designs that call it so, ``architecture``;
+    with neither it is "llama" as in the reference (config.rs:21-22)."""
+    arch = resolve(config.get("model_type") or config.get("architecture") or "llama")
     return arch, arch.parse_config(config)
 
 
@@ -63,3 +64,5 @@ def resolve_folder(folder: str):
 def _ensure_builtin() -> None:
     if "llama" not in _ARCHITECTURES:
         from .models import llama  # noqa: F401  (registers itself)
+    if "Rugesun" not in _ARCHITECTURES:
+        from .models import rugesun  # noqa: F401

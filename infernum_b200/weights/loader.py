@@ -39,7 +39,8 @@ def check_against_specs(specs: Mapping[str, WeightSpec], table: Mapping[str, Ten
     for name, spec in specs.items():
         src = name if name in table else (spec.fallback if spec.fallback in table else None)
         if src is None:
-            missing.append(name)
+            if not spec.optional:
+                missing.append(name)
             continue
         entry = table[src]
         if tuple(entry.shape) != tuple(spec.shape):
@@ -89,6 +90,8 @@ def load_tensors(folder: str, specs: Mapping[str, WeightSpec], engine_dtype: tor
     source = check_against_specs(specs, table, ignorable, strict)
     out: Dict[str, torch.Tensor] = {}
     for name, spec in specs.items():
+        if name not in source:
+            continue  # an optional tensor the files leave out
         entry = table[source[name]]
         cpu = entry.file.read(entry.name)
         dtype = kept_dtype(spec, entry.dtype, engine_dtype)
