@@ -124,7 +124,8 @@ def run_trace_subprocess(model_dir: str, dtype: str, steps: List[dict], out_dir:
 
 
 def read_outputs(out_dir: str, steps: List[dict], model_dir: str) -> Dict[int, np.ndarray]:
-    vocab = json.load(open(os.path.join(model_dir, "config.json")))["vocab_size"]
+    cfg = json.load(open(os.path.join(model_dir, "config.json")))
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     out = {}
     for s in steps:
         wanted = sum(len(e.get("want", [])) for e in s["entries"])
