@@ -39,6 +39,15 @@ def latent_attention(q_abs: torch.Tensor, pool: torch.Tensor, out: torch.Tensor,
     ``q_abs`` [N, heads, kv_rank + rot_dim] holds each head's query in latent
     space followed by its rotated part; the pool [pages, 1, page_size,
     kv_rank + rot_dim] each token's latent followed by the shared rotated key;
-    ``out`` [N, heads, kv_rank] receives the weighted sums of latents."""
+    ``out`` [N, heads, kv_rank] receives the weighted sums of latents.  Rows and
+    heads may lie in any order in memory (strides).  bfloat16 engines take the
+    tensor-core kernel when the sizes have a variant, everything else the plain
+    32-bit kernel; ``rt.options["attention"] = "plain"`` forces the latter."""
+    impl = rt.options.get("attention", "auto")
+    if q_abs.dtype == torch.bfloat16 and impl != "plain":
+        from . import attention_latent
+
+        if attention_latent.run(q_abs, pool, out, kv_rank, ctx, tables, scale, window, rt):
+            return
     core.attention_latent_plain(q_abs, pool, out, kv_rank, ctx.positions, ctx.row_entry, tables, scale,
                                 window, rt.err)

@@ -685,8 +685,7 @@ def attention_latent_plain(q_abs: torch.Tensor, pool: torch.Tensor, out: torch.T
     num_pages, one, page_size, width = pool.shape
     N, heads, qw = q_abs.shape
     if one != 1 or qw != width or q_abs.stride(2) != 1 or out.stride(2) != 1 or out.shape != (N, heads, kv_rank) \
-            or not (q_abs.dtype == pool.dtype == out.dtype) or not pool.is_contiguous() \
-            or q_abs.stride(1) * heads > q_abs.stride(0) or out.stride(1) * heads > out.stride(0):
+            or not (q_abs.dtype == pool.dtype == out.dtype) or not pool.is_contiguous():
         raise KernelError("attention_latent_plain: q_abs [N, heads, width], pool [pages, 1, page, width] and "
                           "out [N, heads, kv_rank] do not fit")
     check(core_lib().ib_attention_plain_ex(q_abs.data_ptr(), q_abs.stride(0), pool.data_ptr(), pool.data_ptr(),

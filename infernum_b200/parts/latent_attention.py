@@ -138,14 +138,16 @@ class LatentAttention(Mixer):
                             self.kv_norm, self.eps, self.inv_freq, ctx.positions, ctx.row_entry,
                             tables if writes else None, cq, pool if writes else None, self.rt.err)
         q = self.uq(cq)
-        q_abs = torch.empty((N, H, W), dtype=x.dtype, device=x.device)
+        # queries in latent space and the sums of latents are kept head by head ([H, N, .]):
+        # the per-head products then read and write plain matrices
+        q_abs = torch.empty((H, N, W), dtype=x.dtype, device=x.device)
         core.latent_q_rotate(q, H, self.dim, self.rot_dim, self.rotary_dim, self.inv_freq, ctx.positions,
-                             q_abs, self.kv_rank)
+                             q_abs.transpose(0, 1), self.kv_rank)
         q3 = q.view(N, H, self.dim + self.rot_dim)
-        batched_matmul_nt(q3[:, :, : self.dim].transpose(0, 1), self.uk_t,
-                          q_abs[:, :, : self.kv_rank].transpose(0, 1))
-        o_lat = torch.empty((N, H, self.kv_rank), dtype=x.dtype, device=x.device)
-        attn_ops.latent_attention(q_abs, pool, o_lat, self.kv_rank, ctx, tables, self.scale, self.window, self.rt)
+        batched_matmul_nt(q3[:, :, : self.dim].transpose(0, 1), self.uk_t, q_abs[:, :, : self.kv_rank])
+        o_lat = torch.empty((H, N, self.kv_rank), dtype=x.dtype, device=x.device)
+        attn_ops.latent_attention(q_abs.transpose(0, 1), pool, o_lat.transpose(0, 1), self.kv_rank, ctx, tables,
+                                  self.scale, self.window, self.rt)
         o = torch.empty((N, H, self.vdim), dtype=x.dtype, device=x.device)
-        batched_matmul_nt(o_lat.transpose(0, 1), self.uv, o.transpose(0, 1))
+        batched_matmul_nt(o_lat, self.uv, o.transpose(0, 1))
         return self.o(o.view(N, H * self.vdim))

@@ -63,8 +63,14 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype]
 def batched_matmul_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out[b] = x[b] @ w[b]^T`` for ``x`` [B, M, K], ``w`` [B, N, K], ``out``
     [B, M, N]; any batch and row strides (the members may be heads lying side by
-    side in the rows of one matrix), inner strides 1.  The package's plain
-    kernel: 32-bit multiply-adds in k order for every dtype."""
+    side in the rows of one matrix), inner strides 1.  bfloat16: the library's
+    batched product (32-bit accumulation); everything else the package's plain
+    kernel, 32-bit multiply-adds in k order."""
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
+        core.require_cuda(x, w, out)
+        torch.bmm(x, w.transpose(1, 2), out=out)
+        core.profile_mark("library_bmm")
+        return out
     core.gemm_plain_batched(x, w, out)
     return out
 

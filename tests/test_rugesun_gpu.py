@@ -490,7 +490,12 @@ def latent_case(dtype, heads, kv_rank, rot_dim, page_size, lengths, new_rows, wi
     return out, ref, rows_e, rows_p
 
 
-KERNELS = [("float32", None), ("bfloat16", {"attention": "plain"}), ("bfloat16", None)]
+# the plain kernel in both dtypes; the tensor-core kernel as its plan comes out, and with the
+# plans forced that the small cases would not choose: one or two row tiles per CTA, keys of a
+# row tile shared out over 3 or 7 CTAs
+KERNELS = [("float32", None), ("bfloat16", {"attention": "plain"}), ("bfloat16", None),
+           ("bfloat16", {"latent_plan": (1, 3)}), ("bfloat16", {"latent_plan": (2, 7)}),
+           ("bfloat16", {"latent_plan": (2, 1)})]
 
 
 @pytest.mark.parametrize("dtype,options", KERNELS)
