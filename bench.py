@@ -248,7 +248,7 @@ def time_e2e(model, batch, prompt_len, steps, warmup, page_size, seed, launch_ah
     return out
 
 
-def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3, recorded=False):
+def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3, recorded=False, flops=None):
     """One step over a whole prompt of ``T`` tokens, timed on the device.
     ``recorded``: the way ``Engine`` runs a prompt that comes alone - replayed from
     a recording made for the bucket of its length - with the host's own time for
@@ -289,7 +289,7 @@ def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3, recorded=False
         cache.release(rc)
     runner.check_errors()
     ms = sorted(times)[len(times) // 2]
-    flops = prefill_flops(cfg, T, layers)
+    flops = flops(T) if flops is not None else prefill_flops(cfg, T, layers)
     peak = peaks["bf16_tflops_sustained"]
     del runner, cache
     torch.cuda.empty_cache()
@@ -298,6 +298,112 @@ def time_prefill(model, cfg, layers, T, page_size, peaks, reps=3, recorded=False
             "peak_tflops": peak,
             # the same against the burst rate of the library product (a kernel timed in isolation)
             "frac_of_burst": flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)}
+
+
+# ---------------------------------------------------------------------------------------------
+# --design rugesun: the Rugesun decoder beside the Llama decoder at equal sizes
+# ---------------------------------------------------------------------------------------------
+def rugesun_config(width, layers, heads, ff, vocab, q_rank, experts=16, top=4, window=4096,
+                   dim=128, rot=64, vdim=128, kv_rank=512):
+    """Layers in fours: two that keep a latent cache (a gated GELU feed-forward, then a
+    mixture of experts) and two that read the second one's cache (the same feed-forwards).
+    An expert has ff / top columns, so a token's chosen experts do a dense layer's work."""
+    def mixer(kv_from=None):
+        m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+             "scale": (dim + rot) ** -0.5, "rot": {"base": 10000.0, "dims": rot}, "mask": {"size": window}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return m
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top}}
+    out = []
+    for i in range(layers):
+        base = i - i % 4
+        kv_from = base + 1 if i % 4 >= 2 else None
+        out.append({"type": "latent_attention", "mixer": mixer(kv_from), "mlp": dense if i % 2 == 0 else moe})
+    return {"architecture": "Rugesun", "vocab": vocab, "width": width, "postln_alpha": 1.0, "logit_softcap": 30.0,
+            "norm": {"eps": 1e-6}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": out, "max_position": 8192}
+
+
+def rugesun_prefill_flops(cfg: dict, T: int) -> float:
+    """Multiply-adds x 2 of one prompt step as the engine computes it (queries taken into
+    latent space, attention over the cached latents), counting a token's chosen experts only."""
+    D, total = cfg["width"], 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        H, d, r, v, kr, qr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+        w = (m.get("mask") or {}).get("size", 0)
+        down = qr + (0 if "kv_from" in m else kr + r)
+        keys = sum(min(t + 1, w) if w else t + 1 for t in range(T))
+        total += 2.0 * T * (D * down + qr * H * (d + r) + H * d * kr + H * kr * v + H * v * D)
+        total += 2.0 * H * (2 * kr + r) * keys
+        mlp = layer["mlp"]
+        if mlp and mlp["kind"] == "dense":
+            total += 6.0 * T * D * mlp["ff"]
+        elif mlp:
+            total += 6.0 * T * D * mlp["expert"]["ff"] * mlp["router"]["top"] + 2.0 * T * D * mlp["router"]["experts"]
+    return total + 2.0 * D * cfg["vocab"]
+
+
+DESIGN_SIZES = {
+    # name: (width, layers, heads, feed-forward, vocabulary, q_rank, llama kv heads)
+    "2b-shape": (2048, 8, 16, 8192, 32000, 768, 4),
+    "8b-shape": (4096, 8, 32, 14336, 32000, 1536, 8),
+}
+
+
+def design_compare(args, peaks) -> dict:
+    """Prefill and decode of the Rugesun decoder at a few sizes, and of the Llama decoder at
+    the same width, depth, heads, feed-forward width and vocabulary."""
+    import gc
+
+    import torch
+
+    import infernum_b200 as ib
+
+    opts = {"sm_count": torch.cuda.get_device_properties(0).multi_processor_count}
+    out = {}
+    for name, (width, layers, heads, ff, vocab, q_rank, kv_heads) in DESIGN_SIZES.items():
+        if args.size and name != args.size:
+            continue
+        if args.layers:
+            layers = args.layers
+        llama = {"model_type": "llama", "num_hidden_layers": layers, "hidden_size": width,
+                 "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": 128,
+                 "intermediate_size": ff, "vocab_size": vocab, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+                 "tie_word_embeddings": False, "max_position_embeddings": 8192}
+        rug = rugesun_config(width, layers, heads, ff, vocab, q_rank)
+        for label, cfg in (("rugesun", rug), ("llama", llama)):
+            if args.only_model and label != args.only_model:
+                continue
+            model = ib.random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0", options=dict(opts))
+            row = {}
+            flops = (lambda T, c=cfg: rugesun_prefill_flops(c, T)) if label == "rugesun" else \
+                (lambda T, c=cfg: prefill_flops(c, T, layers))
+            for T in (512, 2048):
+                if args.only == "decode":
+                    break
+                r = time_prefill(model, cfg, layers, T, args.page_size, peaks, flops=flops)
+                row[f"prefill_{T}_tok_s"] = round(r["value"], 1)
+                row[f"prefill_{T}_ms"] = round(r["ms"], 3)
+                row[f"prefill_{T}_frac_of_sustained_bf16"] = round(r["frac"], 4)
+            for b in (1, 8, 64):
+                if args.only == "prefill":
+                    break
+                r = time_decode(model, b, args.prompt_len, min(args.steps, 64), max(args.warmup, 3), args.page_size,
+                                args.seed + b, graph=not args.no_cuda_graph)
+                row[f"decode_b{b}_tok_s"] = round(r["tokens_per_s"], 1)
+                row[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
+                row[f"decode_b{b}_hbm_frac"] = round(
+                    r["bytes_per_step"] / (r["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+                row[f"decode_b{b}_launches"] = r["launches_per_step"]
+            row["weight_gb"] = round(model.step_weight_bytes() / 1e9, 3)
+            out[f"{name}/{label}"] = row
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+    return out
 
 
 def scheduler_workloads(seed: int) -> dict:
@@ -374,6 +480,11 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print its numbers (for profiling)")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel")
+    ap.add_argument("--design", choices=["rugesun"], default=None,
+                    help="instead of the default workload: prefill and decode of this design at a few sizes,\n"
+                         "beside the Llama decoder at equal sizes; prints one JSON line {\"design\": ...}")
+    ap.add_argument("--size", default=None, help="with --design: one of its sizes only")
+    ap.add_argument("--only-model", default=None, help="with --design: 'rugesun' or 'llama' only")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -392,6 +503,12 @@ def main() -> int:
     from infernum_b200.csrc.build import loaded_libraries
 
     peaks = load_peaks()
+    if args.design:
+        torch.cuda.set_device(0)
+        print(json.dumps({"design": args.design, "dtype": "bf16", "data": "synthetic: seeded random weights",
+                          "prompt_len": args.prompt_len, "peaks": peaks["source"],
+                          "sizes": design_compare(args, peaks)}))
+        return 0
     cfg = dict(LLAMA_8B)
     full_layers = cfg["num_hidden_layers"]
     layers = args.layers or full_layers

@@ -11,10 +11,13 @@
 // elements.  So the rows of a step are packed with their heads on the M side
 // of the MMA - packed row g = row * H + head - and a tile of keys fetched once
 // serves all of them: S = Q K^T and O += P K[:, :KV] from the one tile in
-// shared memory.  A CTA (four warps) owns 16 * MT packed rows of one entry.
-// Per tile of 32 keys each warp computes the scores of eight keys for all the
-// CTA's rows, the scores meet in shared memory, every warp takes the softmax
-// of its rows from there, and adds P V for its quarter of the KV value columns.
+// shared memory.  A CTA has RG groups of four warps; a group owns 16 * MT packed
+// rows of one entry, all groups share the tile of keys.  Per tile of 32 keys each
+// warp computes the scores of eight keys for its group's rows; the scores meet
+// in shared memory, where the threads share out the rows for the softmax
+// (running maximum and denominator per row, P rounded to bf16, all kept in
+// shared memory); then each warp adds P V for its quarter of the KV value
+// columns of its group's rows.
 // Keys come by cp.async into two buffers, a row at a time through the block
 // table; rows outside the request's keys or below every row's window are
 // zero-filled, never read (their pages may belong to someone else by now).
@@ -88,13 +91,21 @@ struct LatentParams {
     unsigned* err;
 };
 
-template <int MT>
-__global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParams p) {
-    constexpr int M = 16 * MT;
+constexpr int LDP = KT + 8;       // row stride of the P tile (bf16)
+
+template <int MT, int RG>
+__global__ void __launch_bounds__(128 * RG) latent_attention_kernel(const LatentParams p) {
+    constexpr int M = 16 * MT * RG;
+    constexpr int THREADS = 128 * RG;
+    constexpr int TPR = THREADS / M;                              // threads that share a row's softmax (8 / MT)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [M][LDK]
     bf16* Ks = Qs + M * LDK;                                      // [2][KT][LDK]
-    float* Ss = reinterpret_cast<float*>(Ks + 2 * KT * LDK);      // [M][LDS]
+    bf16* Ps = Ks + 2 * KT * LDK;                                 // [M][LDP]
+    float* Ss = reinterpret_cast<float*>(Ps + M * LDP);           // [M][LDS]
+    float* m_s = Ss + M * LDS;                                    // [M] running maximum
+    float* l_s = m_s + M;                                         // [M] running denominator
+    float* c_s = l_s + M;                                         // [M] this tile's correction of the sums so far
 
     pdl_trigger();
     pdl_wait();
@@ -103,7 +114,9 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
     const int H = p.heads;
     const int g0 = blockIdx.x * M;                 // first packed row of this CTA
     if (g0 >= rows * H) return;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = (tid >> 5) & 3;               // which eight keys / which quarter of the value columns
+    const int rbase = (tid >> 7) * 16 * MT;        // first row of this warp's group within the CTA's rows
     const int grp = lane >> 2, qd = lane & 3;
     const int pos0 = p.q_start[e];
     const int r_first = g0 / H;
@@ -122,7 +135,7 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
 
     // ---- the queries of the tile into shared memory (rows beyond the entry: zero) ----
     constexpr int CH = W / 8;  // 16-byte pieces per row
-    for (int it = tid; it < M * CH; it += 128) {
+    for (int it = tid; it < M * CH; it += THREADS) {
         const int m = it / CH, c = it % CH;
         const int g = g0 + m;
         bf16* dst = Qs + m * LDK + c * 8;
@@ -135,7 +148,7 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
     }
     auto load_keys = [&](int t, int buf) {
         bf16* base = Ks + buf * KT * LDK;
-        for (int it = tid; it < KT * CH; it += 128) {
+        for (int it = tid; it < KT * CH; it += THREADS) {
             const int kr = it / CH, c = it % CH;
             const int j = t * KT + kr;
             bf16* dst = base + kr * LDK + c * 8;
@@ -158,7 +171,6 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
     cp_async_commit();
 
     float o[MT][NT][4];
-    float m_run[MT][2], l_run[MT][2];
     int row_pos[MT][2];   // position of this thread's two rows per m-tile (-1: no such row)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -168,11 +180,13 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
             for (int k = 0; k < 4; ++k) o[mt][nt][k] = 0.f;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-            m_run[mt][hf] = -INFINITY;
-            l_run[mt][hf] = 0.f;
-            const int g = g0 + mt * 16 + grp + hf * 8;
+            const int g = g0 + rbase + mt * 16 + grp + hf * 8;
             row_pos[mt][hf] = g <= g_last ? pos0 + g / H : -1;
         }
+    }
+    for (int i = tid; i < M; i += THREADS) {
+        m_s[i] = -INFINITY;
+        l_s[i] = 0.f;
     }
 
     for (int t = t_lo; t < t_hi; ++t) {
@@ -202,10 +216,10 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 unsigned a[4];
-                ldsm_x4(a, Qs + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks * 16 + (lane >> 4) * 8);
+                ldsm_x4(a, Qs + (rbase + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + ks * 16 + (lane >> 4) * 8);
                 mma16816(s[mt], a, b[0], b[1]);
                 if (two) {
-                    ldsm_x4(a, Qs + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (ks + 1) * 16 + (lane >> 4) * 8);
+                    ldsm_x4(a, Qs + (rbase + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDK + (ks + 1) * 16 + (lane >> 4) * 8);
                     mma16816(s[mt], a, b[2], b[3]);
                 }
             }
@@ -219,36 +233,54 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
                 const int j = t * KT + warp * 8 + qd * 2 + (k & 1);
                 const int rp = row_pos[mt][hf];
                 const bool seen = rp >= 0 && j <= rp && (p.window <= 0 || j > rp - p.window);
-                Ss[(mt * 16 + grp + hf * 8) * LDS + warp * 8 + qd * 2 + (k & 1)] = seen ? s[mt][k] * p.scale : -INFINITY;
+                Ss[(rbase + mt * 16 + grp + hf * 8) * LDS + warp * 8 + qd * 2 + (k & 1)] = seen ? s[mt][k] * p.scale : -INFINITY;
             }
         __syncthreads();
-        // ---- softmax of this thread's rows, P as A fragments, O += P V --------------
+        // ---- softmax: TPR threads a row; maximum, P (bf16) and denominator into shared memory ----
+        {
+            constexpr int KPT = KT / TPR;   // keys per thread
+            const int row = tid / TPR, sub = tid % TPR;
+            const float* srow = Ss + row * LDS + sub * KPT;
+            float sv[KPT];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < KPT; ++j) {
+                sv[j] = srow[j];
+                mx = fmaxf(mx, sv[j]);
+            }
+#pragma unroll
+            for (int o2 = TPR / 2; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
+            const float m_old = m_s[row];
+            mx = fmaxf(mx, m_old);
+            const float base = mx == -INFINITY ? 0.f : mx;
+            float sum = 0.f;
+            bf16* prow = Ps + row * LDP + sub * KPT;
+#pragma unroll
+            for (int j = 0; j < KPT; j += 2) {
+                const float p0 = __expf(sv[j] - base), p1 = __expf(sv[j + 1] - base);
+                sum += p0 + p1;
+                *reinterpret_cast<__nv_bfloat162*>(prow + j) = __floats2bfloat162_rn(p0, p1);
+            }
+#pragma unroll
+            for (int o2 = TPR / 2; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
+            if (sub == 0) {
+                const float corr = __expf(m_old - base);    // exp(-inf) = 0 before the first seen key
+                c_s[row] = corr;
+                l_s[row] = l_s[row] * corr + sum;
+                m_s[row] = mx;
+            }
+        }
+        __syncthreads();
+        // ---- O += P V for this warp's rows and value columns ---------------------------
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             unsigned pa[2][4];
             float corr[2];
+            corr[0] = c_s[rbase + mt * 16 + grp];
+            corr[1] = c_s[rbase + mt * 16 + grp + 8];
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                const float* srow = Ss + (mt * 16 + grp + hf * 8) * LDS;
-                float mx = m_run[mt][hf];
-#pragma unroll
-                for (int j = 0; j < KT; ++j) mx = fmaxf(mx, srow[j]);
-                const float base = mx == -INFINITY ? 0.f : mx;
-                corr[hf] = __expf(m_run[mt][hf] - base);     // exp(-inf) = 0 before the first seen key
-                m_run[mt][hf] = mx;
-                float sum = 0.f;
-#pragma unroll
-                for (int kk = 0; kk < 2; ++kk) {
-                    const float p0 = __expf(srow[kk * 16 + qd * 2] - base);
-                    const float p1 = __expf(srow[kk * 16 + qd * 2 + 1] - base);
-                    const float p2 = __expf(srow[kk * 16 + 8 + qd * 2] - base);
-                    const float p3 = __expf(srow[kk * 16 + 8 + qd * 2 + 1] - base);
-                    sum += (p0 + p1) + (p2 + p3);
-                    pa[kk][hf] = pack_bf16(p0, p1);          // a0a1 (row g) / a2a3 (row g + 8)
-                    pa[kk][2 + hf] = pack_bf16(p2, p3);      // a4a5 / a6a7
-                }
-                l_run[mt][hf] = l_run[mt][hf] * corr[hf] + sum;   // this thread's columns only; quads are summed at the end
-            }
+            for (int kk = 0; kk < 2; ++kk)
+                ldsm_x4(pa[kk], Ps + (rbase + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 o[mt][nt][0] *= corr[0];
@@ -273,16 +305,16 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
         __syncthreads();   // the key buffer and the score tile are free again
     }
     cp_async_wait<0>();
+    __syncthreads();   // (with no key tile at all the rows' statistics were only just initialised)
 
     // ---- results ------------------------------------------------------------------------
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-            float l = l_run[mt][hf];
-            l += __shfl_xor_sync(0xffffffffu, l, 1);
-            l += __shfl_xor_sync(0xffffffffu, l, 2);
-            const int g = g0 + mt * 16 + grp + hf * 8;
+            const int lr = rbase + mt * 16 + grp + hf * 8;
+            const float l = l_s[lr];
+            const int g = g0 + lr;
             if (g > g_last) continue;
             const int r = g / H, h = g % H;
             if (p.splits <= 1) {
@@ -299,7 +331,7 @@ __global__ void __launch_bounds__(128) latent_attention_kernel(const LatentParam
                 for (int nt = 0; nt < NT; ++nt)
                     *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[mt][nt][hf * 2], o[mt][nt][hf * 2 + 1]);
                 if (warp == 0 && qd == 0) {
-                    p.part_ml[pr * 2] = m_run[mt][hf];
+                    p.part_ml[pr * 2] = m_s[lr];
                     p.part_ml[pr * 2 + 1] = l;
                 }
             }
@@ -333,19 +365,21 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_o, const fl
     }
 }
 
-template <int MT>
-int launch_latent(const LatentParams& p, int tiles_x, cudaStream_t s) {
-    constexpr int M = 16 * MT;
-    const size_t smem = (size_t)(M * LDK + 2 * KT * LDK) * sizeof(bf16) + (size_t)M * LDS * sizeof(float);
+template <int MT, int RG>
+int launch_latent(const LatentParams& p, int max_packed_rows, cudaStream_t s) {
+    constexpr int M = 16 * MT * RG;
+    const size_t smem = (size_t)(M * LDK + 2 * KT * LDK + M * LDP) * sizeof(bf16) +
+                        (size_t)(M * LDS + 3 * M) * sizeof(float);
     static bool set = false;
     if (!set && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<MT, RG>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
-    cudaError_t le = launch_kernel(latent_attention_kernel<MT>, dim3(tiles_x, p.n_entries, p.splits), dim3(128),
-                                   smem, s, p);
+    const int tiles_x = (max_packed_rows + M - 1) / M;
+    cudaError_t le = launch_kernel(latent_attention_kernel<MT, RG>, dim3(tiles_x, p.n_entries, p.splits),
+                                   dim3(128 * RG), smem, s, p);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;
@@ -360,7 +394,8 @@ IB_EXPORT long long ib_attention_latent_scratch_bytes(int n_rows, int heads, int
 }
 
 // q [N, H, W] with row / head strides q_rs / q_hs (elements), out [N, H, KV] likewise; bf16.
-// `mt`: 1 or 2 sixteen-row tiles per CTA.  `splits` > 1 needs scratch of
+// `mt`: packed rows per CTA in sixteens: 1, 2 (four warps) or 4 (eight warps in two groups).
+// `splits` > 1 needs scratch of
 // ib_attention_latent_scratch_bytes.
 IB_EXPORT int ib_attention_latent(const void* q, int q_rs, int q_hs, const void* pool, void* out, int o_rs, int o_hs,
                                   const int* cu_rows, const int* q_start, const int* tables, int max_blocks,
@@ -374,7 +409,7 @@ IB_EXPORT int ib_attention_latent(const void* q, int q_rs, int q_hs, const void*
     if ((q_rs % 8) || (q_hs % 8) || (o_rs % 2) || (o_hs % 2) || ((uintptr_t)q & 15) || ((uintptr_t)pool & 15) ||
         ((uintptr_t)out & 3))
         return IB_ERR_UNSUPPORTED;
-    if (mt != 1 && mt != 2) return IB_ERR_BAD_ARG;
+    if (mt != 1 && mt != 2 && mt != 4) return IB_ERR_BAD_ARG;
     if (n_entries > 65535) return IB_ERR_TOO_LARGE;
     LatentParams p;
     p.q = (const bf16*)q; p.q_rs = q_rs; p.q_hs = q_hs;
@@ -390,9 +425,9 @@ IB_EXPORT int ib_attention_latent(const void* q, int q_rs, int q_hs, const void*
         p.part_ml = p.part_o + (size_t)splits * n_rows * heads * KV;
     }
     cudaStream_t s = (cudaStream_t)stream;
-    const int M = 16 * mt;
-    const int tiles_x = (max_rows_per_entry * heads + M - 1) / M;
-    const int rc = mt == 2 ? launch_latent<2>(p, tiles_x, s) : launch_latent<1>(p, tiles_x, s);
+    const int packed = max_rows_per_entry * heads;
+    const int rc = mt == 4 ? launch_latent<2, 2>(p, packed, s)
+                 : mt == 2 ? launch_latent<2, 1>(p, packed, s) : launch_latent<1, 1>(p, packed, s);
     if (rc != IB_OK) return rc;
     if (splits > 1) {
         cudaError_t le = launch_kernel(latent_combine_kernel, dim3(n_rows * heads), dim3(KV >= 256 ? 128 : 64), 0, s,

@@ -345,8 +345,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                         if (t < p.T) {
                             const float g = __uint_as_float(v[j]);
                             const float u = xch[(c + j) * 64 + row];
-                            ((bf16*)p.out)[(size_t)t * p.ldo + col] =
-                                __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                            // (swiglu 1: SiLU; 2: GELU in its tanh form)
+                            const float a = p.swiglu == 2
+                                ? 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                                : g / (1.f + expf(-g));
+                            ((bf16*)p.out)[(size_t)t * p.ldo + col] = __float2bfloat16_rn(a * u);
                         }
                     }
                 }
@@ -585,7 +588,7 @@ IB_EXPORT int ib_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* o
     p.kblocks_per_split = (kblocks + sp - 1) / sp;
     p.splits = (kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split;  // no empty slice
     p.out_f32 = out_f32;
-    p.swiglu = swiglu ? 1 : 0;
+    p.swiglu = swiglu;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, ldw, BM);
     if (rc != IB_OK) return rc;

@@ -143,6 +143,12 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 // The formula of the other SwiGLU kernels of this package, in float32.
 __device__ __forceinline__ float silu_times(float g, float u) { return g / (1.f + expf(-g)) * u; }
+// The gate's activation times up: act 1 = SiLU, 2 = GELU in its tanh form (the formulas of
+// the stand-alone activation kernel).
+__device__ __forceinline__ float gate_times(float g, float u, int act) {
+    if (act == 2) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return silu_times(g, u);
+}
 
 // Sixteen values of a token's row, bf16, at out[col .. col+16); `limit` ends the row.
 __device__ __forceinline__ void store16(bf16* row, int col, int limit, const float (&v)[16]) {
@@ -166,6 +172,7 @@ struct Params {
     bf16* out;
     unsigned* err;
     int T, N, K, ldo;
+    int act;  // with the gated epilogue: 1 = SiLU, 2 = GELU (tanh form)
     int t_tiles;   // token tiles of 256
     int t_group;   // token tiles of a group: the first region is walked group by group
     int tiles;     // all tiles
@@ -333,7 +340,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         tmem_ld_wait();
                         float v[16];
 #pragma unroll
-                        for (int q = 0; q < 16; ++q) v[q] = silu_times(__uint_as_float(g[q]), __uint_as_float(u[q]));
+                        for (int q = 0; q < 16; ++q) v[q] = gate_times(__uint_as_float(g[q]), __uint_as_float(u[q]), p.act);
                         if (live) store16(row, n0 / 2 + blk * 64 + c, limit, v);
                     }
                 }
@@ -459,6 +466,7 @@ IB_EXPORT int ib_gemm_pair(const void* x, int ldx, const void* w, int ldw, void*
     p.N = N;
     p.K = K;
     p.ldo = ldo;
+    p.act = swiglu;
     p.t_tiles = (T + TILE - 1) / TILE;
     p.t_group = t_group < 1 || t_group > p.t_tiles ? p.t_tiles : t_group;
     const long long all_a = (N + bn_a - 1) / bn_a;

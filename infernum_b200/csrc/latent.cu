@@ -6,7 +6,7 @@
 // [pages, 1, page_size, kv_rank + rot_dim].
 //
 //   latent_prepare   a row of the down projections [ dq : q_rank | dkv : kv_rank | rot : rot_dim ]
-//                    (32-bit) -> c_q = rmsnorm(dq) * wq in the activation dtype;
+//                    (32-bit or the activation dtype) -> c_q = rmsnorm(dq) * wq in the activation dtype;
 //                    c = rmsnorm(dkv) * wkv and r = rotate(rot, position) into the
 //                    token's place in the pool.  Norms and angles in 32-bit.
 //   latent_q_rotate  the rotated part of every head's query, [.. dim | rot_dim ..] per
@@ -19,8 +19,8 @@
 
 using namespace ib;
 
-template <typename T>
-__global__ void latent_prepare_kernel(const float* __restrict__ lat, int lat_stride, int q_rank, int kv_rank,
+template <typename TI, typename T>
+__global__ void latent_prepare_kernel(const TI* __restrict__ lat, int lat_stride, int q_rank, int kv_rank,
                                       int rot_dim, int rd, const T* __restrict__ wq, const T* __restrict__ wkv,
                                       float eps, const float* __restrict__ inv_freq,
                                       const int* __restrict__ positions, const int* __restrict__ row_entry,
@@ -31,14 +31,14 @@ __global__ void latent_prepare_kernel(const float* __restrict__ lat, int lat_str
     pdl_wait();
     __shared__ float scratch[33];
     const int row = blockIdx.x;
-    const float* x = lat + (size_t)row * lat_stride;
+    const TI* x = lat + (size_t)row * lat_stride;
     if (q_rank > 0) {
         float ss = 0.f;
-        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss += x[i] * x[i];
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss += to_f32(x[i]) * to_f32(x[i]);
         ss = block_sum(ss, scratch);
         const float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
         T* o = cq_out + (size_t)row * q_rank;
-        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) o[i] = from_f32<T>(x[i] * inv * to_f32(wq[i]));
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) o[i] = from_f32<T>(to_f32(x[i]) * inv * to_f32(wq[i]));
     }
     if (!write_kv) return;
     const int pos = positions[row];
@@ -51,29 +51,29 @@ __global__ void latent_prepare_kernel(const float* __restrict__ lat, int lat_str
     }
     const int width = kv_rank + rot_dim;
     T* dst = pool + ((size_t)page * page_size + (pos % page_size)) * width;
-    const float* kv = x + q_rank;
+    const TI* kv = x + q_rank;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) ss += kv[i] * kv[i];
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) ss += to_f32(kv[i]) * to_f32(kv[i]);
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)kv_rank + eps);
-    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) dst[i] = from_f32<T>(kv[i] * inv * to_f32(wkv[i]));
-    const float* rt = kv + kv_rank;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32(kv[i]) * inv * to_f32(wkv[i]));
+    const TI* rt = kv + kv_rank;
     const int half = rd / 2;
     for (int i = threadIdx.x; i < rot_dim - half; i += blockDim.x) {
         if (i < half) {
             float sn, cs;
             sincosf((float)pos * inv_freq[i], &sn, &cs);
-            const float u = rt[i], v = rt[i + half];
+            const float u = to_f32(rt[i]), v = to_f32(rt[i + half]);
             dst[kv_rank + i] = from_f32<T>(u * cs - v * sn);
             dst[kv_rank + i + half] = from_f32<T>(v * cs + u * sn);
         } else {
-            dst[kv_rank + i + half] = from_f32<T>(rt[i + half]);
+            dst[kv_rank + i + half] = from_f32<T>(to_f32(rt[i + half]));
         }
     }
 }
 
-// dtype: of c_q, the norm weights and the pool (0 = f32, 1 = bf16).
-IB_EXPORT int ib_latent_prepare(const float* lat, int lat_stride, int q_rank, int kv_rank, int rot_dim, int rd,
+// dtype: of c_q, the norm weights and the pool (0 = f32, 1 = bf16); in_dtype: of `lat`.
+IB_EXPORT int ib_latent_prepare(const void* lat, int in_dtype, int lat_stride, int q_rank, int kv_rank, int rot_dim, int rd,
                                 const void* wq, const void* wkv, float eps, const float* inv_freq,
                                 const int* positions, const int* row_entry, const int* block_tables,
                                 int max_blocks, void* cq_out, void* pool, int dtype, int page_size, int num_pages,
@@ -90,18 +90,15 @@ IB_EXPORT int ib_latent_prepare(const float* lat, int lat_stride, int q_rank, in
     const int widest = q_rank > kv_rank ? q_rank : kv_rank;
     const int threads = widest >= 1024 ? 256 : 128;
     cudaError_t le;
-    if (dtype == 0)
-        le = launch_kernel(latent_prepare_kernel<float>, dim3(n_rows), dim3(threads), 0, s, lat, lat_stride, q_rank,
-                           kv_rank, rot_dim, rd, (const float*)wq, (const float*)wkv, eps, inv_freq, positions,
-                           row_entry, block_tables, max_blocks, (float*)cq_out, (float*)pool, page_size, num_pages,
-                           write_kv, err);
-    else if (dtype == 1)
-        le = launch_kernel(latent_prepare_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, lat, lat_stride, q_rank,
-                           kv_rank, rot_dim, rd, (const bf16*)wq, (const bf16*)wkv, eps, inv_freq, positions,
-                           row_entry, block_tables, max_blocks, (bf16*)cq_out, (bf16*)pool, page_size, num_pages,
-                           write_kv, err);
-    else
-        return IB_ERR_UNSUPPORTED;
+#define IB_PREP(TI, T)                                                                                              \
+    le = launch_kernel(latent_prepare_kernel<TI, T>, dim3(n_rows), dim3(threads), 0, s, (const TI*)lat, lat_stride, \
+                       q_rank, kv_rank, rot_dim, rd, (const T*)wq, (const T*)wkv, eps, inv_freq, positions,         \
+                       row_entry, block_tables, max_blocks, (T*)cq_out, (T*)pool, page_size, num_pages, write_kv, err)
+    if (dtype == 0 && in_dtype == 0) IB_PREP(float, float);
+    else if (dtype == 1 && in_dtype == 0) IB_PREP(float, bf16);
+    else if (dtype == 1 && in_dtype == 1) IB_PREP(bf16, bf16);
+    else return IB_ERR_UNSUPPORTED;
+#undef IB_PREP
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;

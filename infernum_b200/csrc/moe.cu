@@ -10,6 +10,50 @@
 
 using namespace ib;
 
+// Router logits z[n, e] = sum_k x[n, k] w[e, k] in 32-bit: one warp per (row,
+// expert), lanes stride over k, then a fixed tree over the lanes; a row's logits do
+// not depend on the batch.  The product is skinny (a handful of experts, K in the
+// thousands): a tiled product would leave one CTA walking all of K.
+template <typename TX, typename TW>
+__global__ void router_logits_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w, int ldw,
+                                     float* __restrict__ z, int n_rows, int E, int K) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_rows * E) return;
+    const int n = warp / E, e = warp % E;
+    const TX* xr = x + (size_t)n * ldx;
+    const TW* wr = w + (size_t)e * ldw;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(xr[k]), to_f32(wr[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[(size_t)n * E + e] = acc;
+}
+
+IB_EXPORT int ib_router_logits(const void* x, int x_dtype, int ldx, const void* w, int w_dtype, int ldw, float* z,
+                               int n_rows, int E, int K, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !w || !z || E <= 0 || K <= 0 || ldx < K || ldw < K) return IB_ERR_BAD_ARG;
+    const long long warps = (long long)n_rows * E;
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t le;
+    if (x_dtype == 0 && w_dtype == 0)
+        le = launch_kernel(router_logits_kernel<float, float>, dim3(blocks), dim3(256), 0, s, (const float*)x, ldx,
+                           (const float*)w, ldw, z, n_rows, E, K);
+    else if (x_dtype == 1 && w_dtype == 1)
+        le = launch_kernel(router_logits_kernel<bf16, bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)x, ldx,
+                           (const bf16*)w, ldw, z, n_rows, E, K);
+    else if (x_dtype == 1 && w_dtype == 0)
+        le = launch_kernel(router_logits_kernel<bf16, float>, dim3(blocks), dim3(256), 0, s, (const bf16*)x, ldx,
+                           (const float*)w, ldw, z, n_rows, E, K);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
 __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, int E,
                                  int top, int* __restrict__ ids, float* __restrict__ weights,
                                  float* __restrict__ gate) {

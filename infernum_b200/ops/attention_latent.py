@@ -6,7 +6,7 @@ when a model first needs it.
 width a multiple of 16 and at most 576, bfloat16, 16-byte aligned rows); the
 caller then takes the plain kernel.  How a step's rows are spread is worked out
 once per step and layer geometry and kept in ``ctx.scratch``: 16 or 32 packed
-rows (rows x heads) per CTA, and - when those CTAs would leave most SMs idle, as
+rows (rows x heads; or 64 with eight warps) per CTA, and - when those CTAs would leave most SMs idle, as
 with a few decoded rows - the key tiles of each shared out over several CTAs
 whose partial sums a second kernel merges.
 """
@@ -52,13 +52,13 @@ def lib_for(kv_rank: int, width: int) -> ctypes.CDLL:
 
 
 def choose_plan(rows_per_entry, heads: int, max_kv_len: int, window: int, kv_rank: int, sm_count: int) -> Tuple[int, int]:
-    """(sixteen-row tiles per CTA, splits of the keys).  Two tiles per CTA halve
-    what a tile of keys costs per row, and are taken when an entry has the packed
-    rows to fill them.  Splits: while the CTAs leave SMs idle, the keys a CTA
+    """(packed rows per CTA in sixteens: 1, 2 or 4; splits of the keys).  More rows
+    per CTA share a tile of keys among more rows, and are taken when an entry has
+    the packed rows to fill them (4: eight warps in two groups).  Splits: while the CTAs leave SMs idle, the keys a CTA
     walks (at most the window plus its rows) are shared out, each slice keeping
     at least two tiles of keys."""
     most = max(rows_per_entry) * heads if rows_per_entry else heads
-    mt = 2 if most >= 32 else 1
+    mt = 4 if most >= 64 else 2 if most >= 32 else 1
     m = 16 * mt
     ctas = max(1, sum(-(-(r * heads) // m) for r in rows_per_entry if r > 0))
     reach = max_kv_len if window <= 0 else min(max_kv_len, window + max(rows_per_entry, default=1))

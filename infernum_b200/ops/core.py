@@ -94,13 +94,16 @@ def core_lib() -> ctypes.CDLL:
         lib.ib_embed_hashed.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                         _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
                                         _c_ll, _c_ll, _c_ll, _c_void_p, _c_void_p]
-        lib.ib_latent_prepare.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+        lib.ib_latent_prepare.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
                                           _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                                           _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
         lib.ib_latent_q_rotate.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
                                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]
         lib.ib_moe_route.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
                                      _c_int, _c_void_p]
+        lib.ib_router_logits.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
+                                         _c_int, _c_void_p]
+        lib.ib_router_logits.restype = _c_int
         for fn in ("ib_attention_plain_ex", "ib_gemm_plain_batched", "ib_gated_act", "ib_scale_add_norm",
                    "ib_softcap", "ib_embed_hashed", "ib_latent_prepare", "ib_latent_q_rotate", "ib_moe_route"):
             getattr(lib, fn).restype = _c_int
@@ -620,7 +623,8 @@ def latent_prepare(lat: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, r
                    inv_freq: Optional[torch.Tensor], positions: torch.Tensor, row_entry: torch.Tensor,
                    block_tables: Optional[torch.Tensor], cq_out: Optional[torch.Tensor],
                    pool: Optional[torch.Tensor], err: torch.Tensor) -> None:
-    """From the down projections ``lat`` [N, q_rank + kv_rank + rot_dim] (float32):
+    """From the down projections ``lat`` [N, q_rank + kv_rank + rot_dim] (float32 or
+    the activation dtype; the norms and the rotation are 32-bit either way):
     the normed query latent into ``cq_out``, and - with ``pool`` - the normed
     key/value latent and the rotated shared key part into the token's place in
     the pool [pages, 1, page_size, kv_rank + rot_dim]."""
@@ -629,8 +633,8 @@ def latent_prepare(lat: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, r
     _int32(row_entry, "row_entry")
     _int32(block_tables, "block_tables")
     write_kv = pool is not None
-    if lat.dtype != torch.float32 or lat.dim() != 2 or lat.stride(1) != 1:
-        raise KernelError("latent_prepare: the down projections must be float32 rows")
+    if lat.dim() != 2 or lat.stride(1) != 1:
+        raise KernelError("latent_prepare: the down projections must be rows with unit inner stride")
     act = cq_out.dtype if cq_out is not None else pool.dtype
     for t, n, name in ((wq, q_rank, "query"), (wkv if write_kv else None, kv_rank, "key/value")):
         if t is not None and (t.shape != (n,) or t.dtype != act or not t.is_contiguous()):
@@ -646,7 +650,7 @@ def latent_prepare(lat: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, r
         max_blocks = block_tables.shape[1]
         if rotary_dim and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
             raise KernelError("latent_prepare: inv_freq must be float32 [rotary_dim / 2]")
-    check(core_lib().ib_latent_prepare(lat.data_ptr(), lat.stride(0), int(q_rank), int(kv_rank), int(rot_dim),
+    check(core_lib().ib_latent_prepare(lat.data_ptr(), dtype_code(lat.dtype), lat.stride(0), int(q_rank), int(kv_rank), int(rot_dim),
                                        int(rotary_dim), _ptr(wq), _ptr(wkv), float(eps), _ptr(inv_freq),
                                        positions.data_ptr(), row_entry.data_ptr(), _ptr(block_tables), max_blocks,
                                        _ptr(cq_out), _ptr(pool), dtype_code(act), page_size, num_pages,
@@ -729,3 +733,17 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids:
         raise KernelError("moe_route: gate must be contiguous float32 [N, E]")
     check(core_lib().ib_moe_route(logits.data_ptr(), logits.stride(0), _ptr(bias), E, int(top), ids.data_ptr(),
                                   weights.data_ptr(), _ptr(gate), N, stream_ptr(logits)), "moe_route")
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, e] = sum_k x[n, k] w[e, k] in 32-bit, for a handful of experts: one
+    warp per (row, expert), a fixed order of additions."""
+    require_cuda(x, w, out)
+    N, K = x.shape
+    E = w.shape[0]
+    if w.shape[1] != K or out.shape != (N, E) or out.dtype != torch.float32 or not out.is_contiguous() \
+            or x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("router_logits: x [N, K], w [E, K] with unit inner strides, out contiguous float32 [N, E]")
+    check(core_lib().ib_router_logits(x.data_ptr(), dtype_code(x.dtype), x.stride(0), w.data_ptr(),
+                                      dtype_code(w.dtype), w.stride(0), out.data_ptr(), N, E, K, stream_ptr(out)),
+          "router_logits")

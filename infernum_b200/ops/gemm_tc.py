@@ -28,6 +28,9 @@ _pair_lib: Optional[ctypes.CDLL] = None
 _workspaces: Dict[torch.device, dict] = {}
 
 BM, BK = 128, 64
+# the gate's activation in a fused epilogue, as the kernels number them (0: no gated epilogue;
+# ``swiglu=True`` in the calls below is SiLU)
+GATE_CODES = {"silu": 1, "gelu_tanh": 2}
 # What a tile of gemm_pair costs beside its width, in weight rows: its token half is
 # fetched and its prologue and epilogue run whatever the width.
 PAIR_TILE_OVERHEAD = 66
@@ -129,7 +132,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: Optiona
         splits = choose_splits(T, N, K, POLICY["sm_count"])
     code = lib().ib_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
                             out.stride(0), 1 if out.dtype == torch.float32 else 0, T, N, K, splits,
-                            1 if swiglu else 0, (err if err is not None else _error_word(x.device)).data_ptr(),
+                            int(swiglu), (err if err is not None else _error_word(x.device)).data_ptr(),
                             core.stream_ptr(x))
     core.check(code, "gemm_tc")
 
@@ -193,7 +196,7 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
     N = w.shape[0]
     bn_a, cols_a, bn_b = tiling or choose_pair_tiling(T, N, POLICY["sm_count"], swiglu)
     code = pair_lib().ib_gemm_pair(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
-                                   out.stride(0), T, N, K, 1 if swiglu else 0, bn_a, cols_a, bn_b,
+                                   out.stride(0), T, N, K, int(swiglu), bn_a, cols_a, bn_b,
                                    token_group or choose_token_group(T, K), POLICY["sm_count"],
                                    (err if err is not None else _error_word(x.device)).data_ptr(),
                                    core.stream_ptr(x))
@@ -228,18 +231,19 @@ def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor
     the kernel that streams the weights once (decode), prompts to the kernel on
     pairs of SMs when their length suits its tiles (``pair_suits``)."""
     mode = POLICY["mode"]
-    if mode in ("none", "cublas", "library") or activation != "silu":
+    if mode in ("none", "cublas", "library") or activation not in GATE_CODES:
         return False
+    code = GATE_CODES[activation]
     if w_interleaved.shape[0] % 128 or out.dtype != torch.bfloat16:
         return False
     if not eligible(x, w_interleaved, out) or out.stride(0) % 8 or out.data_ptr() % 16:
         return False
     T = x.shape[0]
     if T <= min(POLICY["max_tokens"], 64):
-        gemm_tc(x, w_interleaved, out, splits=1, swiglu=True, err=err)
+        gemm_tc(x, w_interleaved, out, splits=1, swiglu=code, err=err)
         return True
     if pair_suits(T, fused_activation=True):
-        gemm_pair(x, w_interleaved, out, swiglu=True, err=err)
+        gemm_pair(x, w_interleaved, out, swiglu=code, err=err)
         return True
     return False
 

@@ -132,7 +132,7 @@ class LatentAttention(Mixer):
             raise ConfigError("a kv_shared latent attention layer must be scheduled with cache_of")
         tables = ctx.block_tables[cache.group]
         pool = cache.k_pool
-        lat = self.down(x, out_dtype=torch.float32)
+        lat = self.down(x)
         cq = torch.empty((N, self.q_rank), dtype=x.dtype, device=x.device)
         core.latent_prepare(lat, self.q_rank, self.kv_rank, self.rot_dim, self.rotary_dim, self.q_norm,
                             self.kv_norm, self.eps, self.inv_freq, ctx.positions, ctx.row_entry,

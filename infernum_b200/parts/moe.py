@@ -100,7 +100,7 @@ class MixtureOfExperts(FeedForward):
         """(ids [N, top] int32, weights [N, top] float32, gate [N, experts] float32)."""
         n, dev = x.shape[0], x.device
         logits = torch.empty((n, self.experts), dtype=torch.float32, device=dev)
-        core.gemm_plain(x, self.router, logits)  # 32-bit multiply-adds in k order
+        core.router_logits(x, self.router, logits)  # 32-bit multiply-adds, a fixed order per row
         ids = torch.empty((n, self.top), dtype=torch.int32, device=dev)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=dev)
         gate = torch.empty((n, self.experts), dtype=torch.float32, device=dev)
