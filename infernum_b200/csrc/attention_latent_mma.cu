@@ -78,6 +78,12 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+// A barrier of one group of four warps (ids 1, 2: id 0 is __syncthreads): the groups of a CTA
+// meet only around the shared tile of keys and are free of each other in between.
+__device__ __forceinline__ void group_sync(int group) {
+    asm volatile("bar.sync %0, 128;\n" ::"r"(group + 1) : "memory");
+}
+
 struct LatentParams {
     const bf16* q; int q_rs, q_hs;
     const bf16* pool;
@@ -235,7 +241,7 @@ __global__ void __launch_bounds__(128 * RG) latent_attention_kernel(const Latent
                 const bool seen = rp >= 0 && j <= rp && (p.window <= 0 || j > rp - p.window);
                 Ss[(rbase + mt * 16 + grp + hf * 8) * LDS + warp * 8 + qd * 2 + (k & 1)] = seen ? s[mt][k] * p.scale : -INFINITY;
             }
-        __syncthreads();
+        group_sync(tid >> 7);   // (a group's threads take the softmax of the group's own rows)
         // ---- softmax: TPR threads a row; maximum, P (bf16) and denominator into shared memory ----
         {
             constexpr int KPT = KT / TPR;   // keys per thread
@@ -270,23 +276,23 @@ __global__ void __launch_bounds__(128 * RG) latent_attention_kernel(const Latent
                 m_s[row] = mx;
             }
         }
-        __syncthreads();
+        group_sync(tid >> 7);
         // ---- O += P V for this warp's rows and value columns ---------------------------
+        {
+            unsigned pa[MT][2][4];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            unsigned pa[2][4];
-            float corr[2];
-            corr[0] = c_s[rbase + mt * 16 + grp];
-            corr[1] = c_s[rbase + mt * 16 + grp + 8];
+            for (int mt = 0; mt < MT; ++mt) {
+                const float c0 = c_s[rbase + mt * 16 + grp], c1 = c_s[rbase + mt * 16 + grp + 8];
 #pragma unroll
-            for (int kk = 0; kk < 2; ++kk)
-                ldsm_x4(pa[kk], Ps + (rbase + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + kk * 16 + (lane >> 4) * 8);
+                for (int kk = 0; kk < 2; ++kk)
+                    ldsm_x4(pa[mt][kk], Ps + (rbase + mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                o[mt][nt][0] *= corr[0];
-                o[mt][nt][1] *= corr[0];
-                o[mt][nt][2] *= corr[1];
-                o[mt][nt][3] *= corr[1];
+                for (int nt = 0; nt < NT; ++nt) {
+                    o[mt][nt][0] *= c0;
+                    o[mt][nt][1] *= c0;
+                    o[mt][nt][2] *= c1;
+                    o[mt][nt][3] *= c1;
+                }
             }
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
@@ -297,8 +303,11 @@ __global__ void __launch_bounds__(128 * RG) latent_attention_kernel(const Latent
                     int col = warp * (KV / 4) + (nt + (mat >> 1)) * 8;
                     if (nt + 1 >= NT && mat >= 2) col = warp * (KV / 4) + nt * 8;
                     ldsm_x4_trans(v, Kt + (kk * 16 + (mat & 1) * 8 + (lane & 7)) * LDK + col);
-                    mma16816(o[mt][nt], pa[kk], v[0], v[1]);
-                    if (nt + 1 < NT) mma16816(o[mt][nt + 1], pa[kk], v[2], v[3]);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        mma16816(o[mt][nt], pa[mt][kk], v[0], v[1]);
+                        if (nt + 1 < NT) mma16816(o[mt][nt + 1], pa[mt][kk], v[2], v[3]);
+                    }
                 }
             }
         }
@@ -394,7 +403,8 @@ IB_EXPORT long long ib_attention_latent_scratch_bytes(int n_rows, int heads, int
 }
 
 // q [N, H, W] with row / head strides q_rs / q_hs (elements), out [N, H, KV] likewise; bf16.
-// `mt`: packed rows per CTA in sixteens: 1, 2 (four warps) or 4 (eight warps in two groups).
+// `mt`: 1, 2: that many sixteens of packed rows for four warps; 3: 32 rows, 4: 64 rows, for eight
+// warps in two groups.
 // `splits` > 1 needs scratch of
 // ib_attention_latent_scratch_bytes.
 IB_EXPORT int ib_attention_latent(const void* q, int q_rs, int q_hs, const void* pool, void* out, int o_rs, int o_hs,
@@ -409,7 +419,7 @@ IB_EXPORT int ib_attention_latent(const void* q, int q_rs, int q_hs, const void*
     if ((q_rs % 8) || (q_hs % 8) || (o_rs % 2) || (o_hs % 2) || ((uintptr_t)q & 15) || ((uintptr_t)pool & 15) ||
         ((uintptr_t)out & 3))
         return IB_ERR_UNSUPPORTED;
-    if (mt != 1 && mt != 2 && mt != 4) return IB_ERR_BAD_ARG;
+    if (mt < 1 || mt > 4) return IB_ERR_BAD_ARG;
     if (n_entries > 65535) return IB_ERR_TOO_LARGE;
     LatentParams p;
     p.q = (const bf16*)q; p.q_rs = q_rs; p.q_hs = q_hs;
@@ -427,6 +437,7 @@ IB_EXPORT int ib_attention_latent(const void* q, int q_rs, int q_hs, const void*
     cudaStream_t s = (cudaStream_t)stream;
     const int packed = max_rows_per_entry * heads;
     const int rc = mt == 4 ? launch_latent<2, 2>(p, packed, s)
+                 : mt == 3 ? launch_latent<1, 2>(p, packed, s)   // 32 rows in two groups of four warps
                  : mt == 2 ? launch_latent<2, 1>(p, packed, s) : launch_latent<1, 1>(p, packed, s);
     if (rc != IB_OK) return rc;
     if (splits > 1) {
