@@ -73,10 +73,6 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<unsigned*>(&v);
-}
 
 // A barrier of one group of four warps (ids 1, 2: id 0 is __syncthreads): the groups of a CTA
 // meet only around the shared tile of keys and are free of each other in between.
@@ -348,29 +344,45 @@ __global__ void __launch_bounds__(128 * RG) latent_attention_kernel(const Latent
 }
 
 // out[row, head, :] = sum_s exp(m_s - M) O_s / sum_s exp(m_s - M) l_s over the splits.
+// One block per (row, head): the splits' maxima and denominators are fetched side by side
+// (a thread each), turned into one weight per split in shared memory, and every thread then
+// sums its columns over the splits in split order, the loads of a column independent of each
+// other.
 __global__ void latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       bf16* __restrict__ out, int o_rs, int o_hs, int n_rows, int heads,
                                       int splits) {
     pdl_trigger();
     pdl_wait();
+    __shared__ float w_s[64];     // splits <= 64
+    __shared__ float m_sh[64], l_sh[64];
     const int pr = blockIdx.x;   // row * heads + head
     const int r = pr / heads, h = pr % heads;
     const size_t stride = (size_t)n_rows * heads;
-    float mx = -INFINITY;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(s * stride + pr) * 2]);
-    float denom = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float m = part_ml[(s * stride + pr) * 2];
-        if (m > -INFINITY) denom += __expf(m - mx) * part_ml[(s * stride + pr) * 2 + 1];
+    const int tid = threadIdx.x;
+    if (tid < splits) {
+        m_sh[tid] = part_ml[((size_t)tid * stride + pr) * 2];
+        l_sh[tid] = part_ml[((size_t)tid * stride + pr) * 2 + 1];
     }
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
-    for (int c = threadIdx.x; c < KV; c += blockDim.x) {
-        float acc = 0.f;
+    __syncthreads();
+    if (tid == 0) {
+        float mx = -INFINITY;
+        for (int s = 0; s < splits; ++s) mx = fmaxf(mx, m_sh[s]);
+        float denom = 0.f;
         for (int s = 0; s < splits; ++s) {
-            const float m = part_ml[(s * stride + pr) * 2];
-            if (m > -INFINITY) acc += __expf(m - mx) * part_o[(s * stride + pr) * KV + c];
+            const float w = m_sh[s] > -INFINITY ? __expf(m_sh[s] - mx) : 0.f;
+            w_s[s] = w;
+            denom += w * l_sh[s];
         }
-        out[(size_t)r * o_rs + (size_t)h * o_hs + c] = from_f32<bf16>(acc * inv);
+        const float inv = denom > 0.f ? 1.f / denom : 0.f;
+        for (int s = 0; s < splits; ++s) w_s[s] *= inv;
+    }
+    __syncthreads();
+    for (int c = tid; c < KV; c += blockDim.x) {
+        float acc = 0.f;
+        const float* src = part_o + (size_t)pr * KV + c;
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) acc += w_s[s] * src[(size_t)s * stride * KV];
+        out[(size_t)r * o_rs + (size_t)h * o_hs + c] = from_f32<bf16>(acc);
     }
 }
 
@@ -414,7 +426,7 @@ IB_EXPORT int ib_attention_latent(const void* q, int q_rs, int q_hs, const void*
                                   long long scratch_bytes, unsigned* err, void* stream) {
     if (n_entries <= 0 || n_rows <= 0) return IB_OK;
     if (!q || !pool || !out || !cu_rows || !q_start || !tables || !err || heads <= 0 || page_size <= 0 ||
-        num_pages <= 0 || max_blocks <= 0 || max_rows_per_entry <= 0 || splits < 1 || splits > 65535)
+        num_pages <= 0 || max_blocks <= 0 || max_rows_per_entry <= 0 || splits < 1 || splits > 64)
         return IB_ERR_BAD_ARG;
     if ((q_rs % 8) || (q_hs % 8) || (o_rs % 2) || (o_hs % 2) || ((uintptr_t)q & 15) || ((uintptr_t)pool & 15) ||
         ((uintptr_t)out & 3))

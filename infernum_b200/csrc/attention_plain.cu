@@ -115,7 +115,7 @@ IB_EXPORT int ib_attention_plain_ex(const void* q, int q_stride, const void* k_p
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0 ||
         num_pages <= 0 || hdv <= 0 || hdv > v_width || hdv > hd || q_hs < hd || o_hs < hdv)
         return IB_ERR_BAD_ARG;
-    if (hd > 32 * 20) return IB_ERR_TOO_LARGE;
+    if (hd > 32 * 32) return IB_ERR_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
 #define IB_PLAIN(T, NREG)                                                                                   \
     return launch_plain<T, NREG>(q, q_stride, k_pool, v_pool, out, out_stride, positions, row_entry,        \
@@ -123,11 +123,13 @@ IB_EXPORT int ib_attention_plain_ex(const void* q, int q_stride, const void* k_p
                                  scale, hdv, v_width, q_hs, o_hs, err, s)
     if (act_dtype == 0) {
         if (hd <= 256) IB_PLAIN(float, 8);
-        IB_PLAIN(float, 20);
+        if (hd <= 640) IB_PLAIN(float, 20);
+        IB_PLAIN(float, 32);
     }
     if (act_dtype == 1) {
         if (hd <= 256) IB_PLAIN(bf16, 8);
-        IB_PLAIN(bf16, 20);
+        if (hd <= 640) IB_PLAIN(bf16, 20);
+        IB_PLAIN(bf16, 32);
     }
 #undef IB_PLAIN
     return IB_ERR_UNSUPPORTED;

@@ -283,6 +283,36 @@ def test_greedy_generation_through_the_engine(models, name, dtype):
         assert engine.decoder.counts["replayed"] > 0  # the recorded steps were used
 
 
+def test_command_line_generate(models, tmp_path):
+    """``bin/generate`` picks the architecture by config.json: from a model folder, and from
+    a bare configuration with random weights."""
+    import json
+    import subprocess
+    import sys
+
+    from helpers import ROOT
+    folder, plain = models["Asharp"]
+    prompt = [5, 6, 7, 8, 9, 10]
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "-m", folder,
+                          ",".join(map(str, prompt)), "-n", "12", "--greedy", "--dtype", "float32", "--block-size", "4"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("5,6,7,8,9,10")][0]
+    got = [int(t) for t in line.split()[1:]]
+    seq = list(prompt)
+    for tok in got:
+        assert tok == int(torch.argmax(plain.logits(seq)[-1]))
+        seq.append(tok)
+    assert len(got) == 12
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(CASES["B"]))
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), "--config", str(cfg_path),
+                          "--random-weights", "--weights-seed", "3", "1,2,3", "-n", "4", "--greedy",
+                          "--block-size", "8"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert "Generated 4 tokens" in out.stdout
+
+
 # ---- mechanisms alone -------------------------------------------------------------------
 def step_context(cache, requests, tokens=None):
     from types import SimpleNamespace
