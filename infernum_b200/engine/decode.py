@@ -42,6 +42,7 @@ rebuild and run eagerly every step (:1549-1598).
 from __future__ import annotations
 
 import collections
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -293,8 +294,18 @@ class DecodeRunner:
         elif self.use_graph and slot.eager_steps >= 1:
             torch.cuda.synchronize(self.rt.device)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self._body(slot, device_feed)
+            # While a stream records, a call that is not allowed into a recording ends it with an
+            # error, whoever makes the call: a collection of garbage that frees pinned memory or
+            # another recording in the middle of this one, or another thread of the process.  The
+            # collector rests while the step is recorded, and only this thread's calls count.
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    self._body(slot, device_feed)
+            finally:
+                if collecting:
+                    gc.enable()
             slot.graph = graph
             graph.replay()
             self.counts["recorded"] += 1
