@@ -108,6 +108,7 @@ __global__ void __launch_bounds__(128 * RG) latent_attention_kernel(const Latent
     float* m_s = Ss + M * LDS;                                    // [M] running maximum
     float* l_s = m_s + M;                                         // [M] running denominator
     float* c_s = l_s + M;                                         // [M] this tile's correction of the sums so far
+    int* slot_s = reinterpret_cast<int*>(c_s + M);                // [2][KT] where the key rows of a tile lie in the pool
 
     pdl_trigger();
     pdl_wait();
@@ -148,23 +149,29 @@ __global__ void __launch_bounds__(128 * RG) latent_attention_kernel(const Latent
             *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
     }
+    // Where each key row of a tile lies in the pool is looked up once per tile (a thread a
+    // row) and passed through shared memory: a look-up per 16-byte piece would put a
+    // dependent load from the block table before every copy.
     auto load_keys = [&](int t, int buf) {
+        if (tid < KT) {
+            const int j = t * KT + tid;
+            int slot = -1;   // the token's place in the pool, or -1: the row is zero-filled
+            if (j >= key_lo && j <= key_hi) {
+                const int blk = j / p.page_size;
+                const int page = blk < p.max_blocks ? table[blk] : -1;
+                if (page < 0 || page >= p.num_pages) atomicOr(p.err, IB_FLAG_BAD_PAGE);
+                else slot = page * p.page_size + (j % p.page_size);
+            }
+            slot_s[buf * KT + tid] = slot;
+        }
+        __syncthreads();
         bf16* base = Ks + buf * KT * LDK;
         for (int it = tid; it < KT * CH; it += THREADS) {
             const int kr = it / CH, c = it % CH;
-            const int j = t * KT + kr;
             bf16* dst = base + kr * LDK + c * 8;
-            int page = -1;
-            if (j >= key_lo && j <= key_hi) {
-                const int blk = j / p.page_size;
-                page = blk < p.max_blocks ? table[blk] : -1;
-                if (page < 0 || page >= p.num_pages) {
-                    if (c == 0) atomicOr(p.err, IB_FLAG_BAD_PAGE);
-                    page = -1;
-                }
-            }
-            if (page >= 0)
-                cp_async16(dst, p.pool + ((size_t)page * p.page_size + (j % p.page_size)) * W + c * 8);
+            const int slot = slot_s[buf * KT + kr];
+            if (slot >= 0)
+                cp_async16(dst, p.pool + (size_t)slot * W + c * 8);
             else
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
         }
@@ -377,12 +384,22 @@ __global__ void latent_combine_kernel(const float* __restrict__ part_o, const fl
         for (int s = 0; s < splits; ++s) w_s[s] *= inv;
     }
     __syncthreads();
-    for (int c = tid; c < KV; c += blockDim.x) {
-        float acc = 0.f;
+    // four columns a thread, 16 bytes a load (KV is a multiple of 32, the scratch 16-byte aligned)
+    for (int c = tid * 4; c < KV; c += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* src = part_o + (size_t)pr * KV + c;
 #pragma unroll 8
-        for (int s = 0; s < splits; ++s) acc += w_s[s] * src[(size_t)s * stride * KV];
-        out[(size_t)r * o_rs + (size_t)h * o_hs + c] = from_f32<bf16>(acc);
+        for (int s = 0; s < splits; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(src + (size_t)s * stride * KV);
+            const float w = w_s[s];
+            acc.x += w * v.x;
+            acc.y += w * v.y;
+            acc.z += w * v.z;
+            acc.w += w * v.w;
+        }
+        bf16* dst = out + (size_t)r * o_rs + (size_t)h * o_hs + c;
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x, acc.y);
+        *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z, acc.w);
     }
 }
 
@@ -390,7 +407,7 @@ template <int MT, int RG>
 int launch_latent(const LatentParams& p, int max_packed_rows, cudaStream_t s) {
     constexpr int M = 16 * MT * RG;
     const size_t smem = (size_t)(M * LDK + 2 * KT * LDK + M * LDP) * sizeof(bf16) +
-                        (size_t)(M * LDS + 3 * M) * sizeof(float);
+                        (size_t)(M * LDS + 3 * M) * sizeof(float) + (size_t)2 * KT * sizeof(int);
     static bool set = false;
     if (!set && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<MT, RG>,

@@ -29,33 +29,49 @@ __global__ void latent_prepare_kernel(const TI* __restrict__ lat, int lat_stride
                                       unsigned* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float scratch[33];
+    __shared__ float scratch[64];
     const int row = blockIdx.x;
     const TI* x = lat + (size_t)row * lat_stride;
+    const TI* kv = x + q_rank;
+    // the token's place in the pool first: the look-up runs under the sums
+    int pos = 0, page = -1;
+    if (write_kv) {
+        pos = positions[row];
+        const int blk = pos / page_size;
+        page = blk < max_blocks ? block_tables[(size_t)row_entry[row] * max_blocks + blk] : -1;
+    }
+    // both sums of squares in one pass and one barrier; the order of the additions is fixed
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) sq += to_f32(x[i]) * to_f32(x[i]);
+    if (write_kv)
+        for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) sk += to_f32(kv[i]) * to_f32(kv[i]);
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    if (lane == 0) {
+        scratch[warp] = sq;
+        scratch[32 + warp] = sk;
+    }
+    __syncthreads();
+    sq = 0.f;
+    sk = 0.f;
+    for (int w = 0; w < nwarps; ++w) {
+        sq += scratch[w];
+        sk += scratch[32 + w];
+    }
     if (q_rank > 0) {
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) ss += to_f32(x[i]) * to_f32(x[i]);
-        ss = block_sum(ss, scratch);
-        const float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
+        const float inv = 1.f / sqrtf(sq / (float)q_rank + eps);
         T* o = cq_out + (size_t)row * q_rank;
         for (int i = threadIdx.x; i < q_rank; i += blockDim.x) o[i] = from_f32<T>(to_f32(x[i]) * inv * to_f32(wq[i]));
     }
     if (!write_kv) return;
-    const int pos = positions[row];
-    const int e = row_entry[row];
-    const int blk = pos / page_size;
-    const int page = blk < max_blocks ? block_tables[(size_t)e * max_blocks + blk] : -1;
     if (page < 0 || page >= num_pages) {  // the whole block takes this branch
         if (threadIdx.x == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
         return;
     }
     const int width = kv_rank + rot_dim;
     T* dst = pool + ((size_t)page * page_size + (pos % page_size)) * width;
-    const TI* kv = x + q_rank;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) ss += to_f32(kv[i]) * to_f32(kv[i]);
-    ss = block_sum(ss, scratch);
-    const float inv = 1.f / sqrtf(ss / (float)kv_rank + eps);
+    const float inv = 1.f / sqrtf(sk / (float)kv_rank + eps);
     for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32(kv[i]) * inv * to_f32(wkv[i]));
     const TI* rt = kv + kv_rank;
     const int half = rd / 2;
