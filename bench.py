@@ -321,8 +321,8 @@ def rugesun_config(width, layers, heads, ff, vocab, q_rank, experts=16, top=4, w
         base = i - i % 4
         kv_from = base + 1 if i % 4 >= 2 else None
         out.append({"type": "latent_attention", "mixer": mixer(kv_from), "mlp": dense if i % 2 == 0 else moe})
-    return {"architecture": "Rugesun", "vocab": vocab, "width": width, "postln_alpha": 1.0, "logit_softcap": 30.0,
-            "norm": {"eps": 1e-6}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+    return {"architecture": "Rugesun", "vocab": vocab, "width": width, "postln_alpha": 1.0, "logit_softcap": 25.0,
+            "norm": {"eps": 1e-6}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 37, "mul_cur": 19}},
             "layers": out, "max_position": 8192}
 
 
