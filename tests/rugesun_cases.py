@@ -55,7 +55,7 @@ CASE_B = {
 # Sizes the tensor-core kernels take (multiples of 16, pages of 16), a window that is no
 # multiple of a page or a key tile, two owners with readers in between.
 CASE_C = {
-    "architecture": "Rugesun", "vocab": 384, "width": 128, "postln_alpha": 1.25, "logit_softcap": 20.0,
+    "architecture": "Rugesun", "vocab": 384, "width": 128, "postln_alpha": 2.5, "logit_softcap": 20.0,
     "norm": {"eps": 1e-6}, "embedding": {"bigram": {"buckets": 509, "mul_prev": 29, "mul_cur": 11}},
     "layers": [
         layer(mixer(4, 16, 16, 16, 48, 32, 0.18, 37), DENSE(192)),
