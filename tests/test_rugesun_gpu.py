@@ -537,7 +537,8 @@ KERNELS = [("float32", None), ("bfloat16", {"attention": "plain"}), ("bfloat16",
 
 @pytest.mark.parametrize("dtype,options", KERNELS)
 @pytest.mark.parametrize("heads,kv_rank,rot_dim,page", [(3, 40, 8, 4), (8, 64, 16, 16), (1, 20, 4, 8),
-                                                         (16, 128, 64, 16), (5, 96, 32, 32)])
+                                                         (16, 128, 64, 16), (5, 96, 32, 32), (2, 32, 16, 8),
+                                                         (4, 64, 48, 16)])
 def test_keys_just_inside_and_outside_the_window_in_prompts_and_decoding(dtype, options, heads, kv_rank,
                                                                          rot_dim, page):
     window = 37
