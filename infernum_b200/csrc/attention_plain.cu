@@ -30,7 +30,7 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, int q_stride,
                                        const int* __restrict__ block_tables, int max_blocks,
                                        int nh, int nkv, int hd, int page_size, int num_pages,
                                        int window, float scale, int hdv, int v_width, int q_hs, int o_hs,
-                                       unsigned* __restrict__ err) {
+                                       const float* __restrict__ sink, unsigned* __restrict__ err) {
     const int row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -77,6 +77,15 @@ __global__ void attention_plain_kernel(const T* __restrict__ q, int q_stride,
         }
         m = m_new;
     }
+    if (sink) {
+        // a learned logit per head that takes part in the denominator only: no key, no value, not scaled
+        const float sk = sink[head];
+        const float m_new = fmaxf(m, sk);
+        const float corr = expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int i = 0; i < PLAIN_MAX_REGS; ++i) acc[i] *= corr;
+    }
     T* op = out + (size_t)row * out_stride + (size_t)head * o_hs;
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -90,25 +99,26 @@ template <typename T, int NREG>
 static int launch_plain(const void* q, int q_stride, const void* k_pool, const void* v_pool, void* out,
                         int out_stride, const int* positions, const int* row_entry, const int* block_tables,
                         int max_blocks, int n_rows, int nh, int nkv, int hd, int page_size, int num_pages,
-                        int window, float scale, int hdv, int v_width, int q_hs, int o_hs, unsigned* err,
-                        cudaStream_t s) {
+                        int window, float scale, int hdv, int v_width, int q_hs, int o_hs, const float* sink,
+                        unsigned* err, cudaStream_t s) {
     const int warps = 4;
     dim3 grid(n_rows, (nh + warps - 1) / warps);
     attention_plain_kernel<T, NREG><<<grid, warps * 32, 0, s>>>(
         (const T*)q, q_stride, (const T*)k_pool, (const T*)v_pool, (T*)out, out_stride, positions, row_entry,
-        block_tables, max_blocks, nh, nkv, hd, page_size, num_pages, window, scale, hdv, v_width, q_hs, o_hs, err);
+        block_tables, max_blocks, nh, nkv, hd, page_size, num_pages, window, scale, hdv, v_width, q_hs, o_hs, sink, err);
     IB_LAUNCH_CHECK();
     return IB_OK;
 }
 
 // The general form: values of `hdv` elements in rows of `v_width`, query heads
-// `q_hs` and output heads `o_hs` elements apart.
+// `q_hs` and output heads `o_hs` elements apart; `sink` (optional, float32 [nh])
+// adds exp(sink[head]) to each softmax denominator.
 IB_EXPORT int ib_attention_plain_ex(const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                     void* out, int out_stride, int act_dtype, const int* positions,
                                     const int* row_entry, const int* block_tables, int max_blocks, int n_rows,
                                     int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                                    float scale, int hdv, int v_width, int q_hs, int o_hs, unsigned* err,
-                                    void* stream) {
+                                    float scale, int hdv, int v_width, int q_hs, int o_hs, const float* sink,
+                                    unsigned* err, void* stream) {
     if (n_rows <= 0) return IB_OK;
     if (!q || !k_pool || !v_pool || !out || !positions || !row_entry || !block_tables || !err)
         return IB_ERR_BAD_ARG;
@@ -120,7 +130,7 @@ IB_EXPORT int ib_attention_plain_ex(const void* q, int q_stride, const void* k_p
 #define IB_PLAIN(T, NREG)                                                                                   \
     return launch_plain<T, NREG>(q, q_stride, k_pool, v_pool, out, out_stride, positions, row_entry,        \
                                  block_tables, max_blocks, n_rows, nh, nkv, hd, page_size, num_pages, window, \
-                                 scale, hdv, v_width, q_hs, o_hs, err, s)
+                                 scale, hdv, v_width, q_hs, o_hs, sink, err, s)
     if (act_dtype == 0) {
         if (hd <= 256) IB_PLAIN(float, 8);
         if (hd <= 640) IB_PLAIN(float, 20);
@@ -143,5 +153,5 @@ IB_EXPORT int ib_attention_plain(const void* q, int q_stride, const void* k_pool
                                  float scale, unsigned* err, void* stream) {
     return ib_attention_plain_ex(q, q_stride, k_pool, v_pool, out, out_stride, act_dtype, positions, row_entry,
                                  block_tables, max_blocks, n_rows, nh, nkv, hd, page_size, num_pages, window,
-                                 scale, hd, hd, hd, hd, err, stream);
+                                 scale, hd, hd, hd, hd, nullptr, err, stream);
 }

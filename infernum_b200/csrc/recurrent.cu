@@ -1,0 +1,369 @@
+// Kernels around recurrent mixers (a state carried from token to token per
+// request) and around attention with normed queries and keys and an output gate.
+// The scans themselves are in scan.cu.  A step's rows are grouped in entries
+// (one request's next tokens, in order): row_entry[row], cu_rows[entry],
+// slot_ids[entry] live on the device, and a request's state is row `slot` of a
+// float32 state tensor whose rows are `state_stride` floats apart.
+//
+//   token shift    m_j[t] = h_t + (h_{t-1} - h_t) * mu_j        j = 0 .. M-1
+//                  h_{-1} of an entry's first row is the request's state, which
+//                  then takes the entry's last row
+//   causal conv    c_t[ch] = silu(b[ch] + sum_j w[ch][j] x_{t-(taps-1-j)}[ch]),
+//                  inputs before the entry from the state (the last taps-1 inputs)
+//   head norm      out = o / rms_head(o) * w * silu(g)          (rms over one head)
+//   gated norm     v = y * silu(z); out = v / rms_group(v) * w   (rms over a group)
+//   qk norm        q, k <- x / rms(x) * w per head; the normed key and the key
+//                  as projected (the value) go to their pages
+// All arithmetic is 32-bit; small parameter vectors are float32.
+#include "common.cuh"
+
+using namespace ib;
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.f + expf(-g)); }
+
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void token_shift_kernel(const T* __restrict__ x, const float* __restrict__ mu, float* __restrict__ state,
+                                   long long state_stride, const int* __restrict__ row_entry,
+                                   const int* __restrict__ cu_rows, const int* __restrict__ slot_ids,
+                                   T* __restrict__ out, int n_rows, int D, int M) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int e = row_entry[row];
+    const int first = cu_rows[e], last = cu_rows[e + 1] - 1;
+    float* prev = state + (long long)slot_ids[e] * state_stride;
+    const T* xr = x + (size_t)row * D;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float h = to_f32(xr[c]);
+        float hp;
+        if (row == first) {
+            hp = prev[c];
+            prev[c] = to_f32(x[(size_t)last * D + c]);  // (only this thread reads prev[c] of this entry)
+        } else {
+            hp = to_f32(xr[c - D]);
+        }
+        const float d = hp - h;
+        for (int m = 0; m < M; ++m)
+            out[((size_t)m * n_rows + row) * D + c] = from_f32<T>(h + d * mu[(size_t)m * D + c]);
+    }
+}
+
+IB_EXPORT int ib_token_shift(const void* x, int act_dtype, const float* mu, float* state, long long state_stride,
+                             const int* row_entry, const int* cu_rows, const int* slot_ids, void* out, int n_rows,
+                             int D, int M, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !mu || !state || !row_entry || !cu_rows || !slot_ids || !out || D <= 0 || M <= 0) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = D >= 1024 ? 256 : 128;
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(token_shift_kernel<float>, dim3(n_rows), dim3(threads), 0, s, (const float*)x, mu, state,
+                           state_stride, row_entry, cu_rows, slot_ids, (float*)out, n_rows, D, M);
+    else if (act_dtype == 1)
+        le = launch_kernel(token_shift_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, (const bf16*)x, mu, state,
+                           state_stride, row_entry, cu_rows, slot_ids, (bf16*)out, n_rows, D, M);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+#define IB_MAX_TAPS 16
+
+template <typename T>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
+                                        const float* __restrict__ b, const float* __restrict__ state,
+                                        long long state_stride, const int* __restrict__ row_entry,
+                                        const int* __restrict__ cu_rows, const int* __restrict__ slot_ids,
+                                        T* __restrict__ out, int C, int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int e = row_entry[row];
+    const int first = cu_rows[e];
+    const float* st = state + (long long)slot_ids[e] * state_stride;  // [taps-1][C], the newest last
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float acc = b ? b[c] : 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int src = row - (taps - 1 - j);
+            float v;
+            if (src >= first) v = to_f32(x[(size_t)src * x_stride + c]);
+            else v = st[(size_t)(taps - 1 - (first - src)) * C + c];
+            acc += w[(size_t)c * taps + j] * v;
+        }
+        out[(size_t)row * C + c] = from_f32<T>(silu_f(acc));
+    }
+}
+
+// The state after the step: the last taps-1 inputs of (old state ++ the entry's rows).
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ x, int x_stride, float* __restrict__ state,
+                                  long long state_stride, const int* __restrict__ cu_rows,
+                                  const int* __restrict__ slot_ids, int C, int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int e = blockIdx.x;
+    const int first = cu_rows[e], n = cu_rows[e + 1] - first;
+    if (n <= 0) return;
+    float* st = state + (long long)slot_ids[e] * state_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float nv[IB_MAX_TAPS];
+        for (int k = 0; k < taps - 1; ++k) {
+            const int idx = n - (taps - 1 - k);  // place among the entry's rows; negative: in the old state
+            nv[k] = idx >= 0 ? to_f32(x[(size_t)(first + idx) * x_stride + c]) : st[(size_t)(taps - 1 + idx) * C + c];
+        }
+        for (int k = 0; k < taps - 1; ++k) st[(size_t)k * C + c] = nv[k];
+    }
+}
+
+IB_EXPORT int ib_causal_conv_silu(const void* x, int x_stride, int act_dtype, const float* w, const float* b,
+                                  float* state, long long state_stride, const int* row_entry, const int* cu_rows,
+                                  const int* slot_ids, void* out, int n_rows, int n_entries, int C, int taps,
+                                  void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !w || !state || !row_entry || !cu_rows || !slot_ids || !out || C <= 0 || taps <= 0 ||
+        taps > IB_MAX_TAPS || n_entries <= 0)
+        return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 128;
+    const int gy = min(64, (C + threads - 1) / threads);
+    cudaError_t le;
+    if (act_dtype == 0) {
+        le = launch_kernel(causal_conv_silu_kernel<float>, dim3(n_rows, gy), dim3(threads), 0, s, (const float*)x,
+                           x_stride, w, b, (const float*)state, state_stride, row_entry, cu_rows, slot_ids,
+                           (float*)out, C, taps);
+        if (le == cudaSuccess && taps > 1)
+            le = launch_kernel(conv_state_kernel<float>, dim3(n_entries, gy), dim3(threads), 0, s, (const float*)x,
+                               x_stride, state, state_stride, cu_rows, slot_ids, C, taps);
+    } else if (act_dtype == 1) {
+        le = launch_kernel(causal_conv_silu_kernel<bf16>, dim3(n_rows, gy), dim3(threads), 0, s, (const bf16*)x,
+                           x_stride, w, b, (const float*)state, state_stride, row_entry, cu_rows, slot_ids,
+                           (bf16*)out, C, taps);
+        if (le == cudaSuccess && taps > 1)
+            le = launch_kernel(conv_state_kernel<bf16>, dim3(n_entries, gy), dim3(threads), 0, s, (const bf16*)x,
+                               x_stride, state, state_stride, cu_rows, slot_ids, C, taps);
+    } else {
+        return IB_ERR_UNSUPPORTED;
+    }
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// One warp per (row, head): out = o / sqrt(mean_head(o^2) + eps) * w * silu(g).
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ g, int g_stride,
+                                      const float* __restrict__ w, T* __restrict__ out, int n_rows, int heads, int K,
+                                      float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)n_rows * heads) return;
+    const int row = (int)(item / heads), head = (int)(item % heads);
+    const float* op = o + ((size_t)row * heads + head) * K;
+    float ss = 0.f;
+    for (int i = lane; i < K; i += 32) ss += op[i] * op[i];
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)K + eps);
+    const T* gp = g ? g + (size_t)row * g_stride + (size_t)head * K : nullptr;
+    T* dst = out + ((size_t)row * heads + head) * K;
+    for (int i = lane; i < K; i += 32) {
+        float v = op[i] * inv * w[(size_t)head * K + i];
+        if (gp) v *= silu_f(to_f32(gp[i]));
+        dst[i] = from_f32<T>(v);
+    }
+}
+
+IB_EXPORT int ib_head_norm_gate(const float* o, const void* g, int g_stride, int act_dtype, const float* w, void* out,
+                                int n_rows, int heads, int K, float eps, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!o || !w || !out || heads <= 0 || K <= 0 || !(eps > 0.f)) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long items = (long long)n_rows * heads;
+    const unsigned grid = (unsigned)((items + 3) / 4);
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(head_norm_gate_kernel<float>, dim3(grid), dim3(128), 0, s, o, (const float*)g, g_stride, w,
+                           (float*)out, n_rows, heads, K, eps);
+    else if (act_dtype == 1)
+        le = launch_kernel(head_norm_gate_kernel<bf16>, dim3(grid), dim3(128), 0, s, o, (const bf16*)g, g_stride, w,
+                           (bf16*)out, n_rows, heads, K, eps);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// One block per (row, group): v = y * silu(z); out = v / sqrt(mean_group(v^2) + eps) * w.
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, int z_stride,
+                                        const float* __restrict__ w, T* __restrict__ out, int inner, int group,
+                                        float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int row = blockIdx.x, g0 = blockIdx.y * group;
+    const float* yp = y + (size_t)row * inner + g0;
+    const T* zp = z + (size_t)row * z_stride + g0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+        const float v = yp[i] * silu_f(to_f32(zp[i]));
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)group + eps);
+    for (int i = threadIdx.x; i < group; i += blockDim.x) {
+        const float v = yp[i] * silu_f(to_f32(zp[i]));
+        out[(size_t)row * inner + g0 + i] = from_f32<T>(v * inv * w[g0 + i]);
+    }
+}
+
+IB_EXPORT int ib_gated_group_norm(const float* y, const void* z, int z_stride, int act_dtype, const float* w,
+                                  void* out, int n_rows, int inner, int groups, float eps, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!y || !z || !w || !out || inner <= 0 || groups <= 0 || inner % groups || !(eps > 0.f)) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int group = inner / groups;
+    const int threads = group >= 2048 ? 512 : (group >= 512 ? 256 : 128);
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(gated_group_norm_kernel<float>, dim3(n_rows, groups), dim3(threads), 0, s, y,
+                           (const float*)z, z_stride, w, (float*)out, inner, group, eps);
+    else if (act_dtype == 1)
+        le = launch_kernel(gated_group_norm_kernel<bf16>, dim3(n_rows, groups), dim3(threads), 0, s, y,
+                           (const bf16*)z, z_stride, w, (bf16*)out, inner, group, eps);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Query/key norm and the write of keys and values into their pages.  x rows
+// hold nh query heads followed by nkv key heads of hd values.  One warp per
+// (row, head).  Queries are normed in place.  A key is written normed to the
+// key pool; the value pool gets the key as projected (value_from_key) or the
+// value head found `v_off` elements into the row.
+template <typename T>
+__global__ void qk_norm_append_kernel(T* __restrict__ x, int x_stride, const float* __restrict__ qw,
+                                      const float* __restrict__ kw, float eps, const int* __restrict__ positions,
+                                      const int* __restrict__ row_entry, const int* __restrict__ block_tables,
+                                      int max_blocks, T* __restrict__ k_pool, T* __restrict__ v_pool, int n_rows,
+                                      int nh, int nkv, int hd, int v_off, int page_size, int num_pages,
+                                      unsigned* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int per_row = nh + nkv;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)n_rows * per_row) return;
+    const int row = (int)(item / per_row), head = (int)(item % per_row);
+    T* p = x + (size_t)row * x_stride + (size_t)head * hd;
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+        const float v = to_f32(p[i]);
+        ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)hd + eps);
+    if (head < nh) {
+        for (int i = lane; i < hd; i += 32) {
+            float v = to_f32(p[i]);
+            if (qw) v = v * inv * qw[i];
+            p[i] = from_f32<T>(v);
+        }
+        return;
+    }
+    const int g = head - nh;
+    const int pos = positions[row], e = row_entry[row];
+    const int slot_idx = pos / page_size;
+    const int page = (pos >= 0 && slot_idx < max_blocks) ? block_tables[(size_t)e * max_blocks + slot_idx] : -1;
+    if (page < 0 || page >= num_pages) {
+        if (lane == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
+        return;
+    }
+    const size_t at = (((size_t)page * nkv + g) * page_size + (pos % page_size)) * hd;
+    const T* vsrc = v_off >= 0 ? x + (size_t)row * x_stride + v_off + (size_t)g * hd : p;
+    for (int i = lane; i < hd; i += 32) {
+        const float raw = to_f32(p[i]);
+        v_pool[at + i] = vsrc[i];
+        k_pool[at + i] = from_f32<T>(kw ? raw * inv * kw[i] : raw);
+    }
+}
+
+IB_EXPORT int ib_qk_norm_append(void* x, int x_stride, int act_dtype, const float* qw, const float* kw, float eps,
+                                const int* positions, const int* row_entry, const int* block_tables, int max_blocks,
+                                void* k_pool, void* v_pool, int n_rows, int nh, int nkv, int hd, int v_off,
+                                int page_size, int num_pages, unsigned* err, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !positions || !row_entry || !block_tables || !k_pool || !v_pool || !err || nh <= 0 || nkv <= 0 ||
+        hd <= 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !(eps > 0.f))
+        return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long items = (long long)n_rows * (nh + nkv);
+    const unsigned grid = (unsigned)((items + 3) / 4);
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(qk_norm_append_kernel<float>, dim3(grid), dim3(128), 0, s, (float*)x, x_stride, qw, kw, eps,
+                           positions, row_entry, block_tables, max_blocks, (float*)k_pool, (float*)v_pool, n_rows, nh,
+                           nkv, hd, v_off, page_size, num_pages, err);
+    else if (act_dtype == 1)
+        le = launch_kernel(qk_norm_append_kernel<bf16>, dim3(grid), dim3(128), 0, s, (bf16*)x, x_stride, qw, kw, eps,
+                           positions, row_entry, block_tables, max_blocks, (bf16*)k_pool, (bf16*)v_pool, n_rows, nh,
+                           nkv, hd, v_off, page_size, num_pages, err);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Elementwise: op 0: a <- a * sigmoid(b)   (an output gate)
+//              op 1: a <- ca * a + cb * b  (two mixers side by side)
+//              op 2: a <- tanh(a)
+// a is [rows, cols] contiguous, b has rows `b_stride` apart.
+template <typename T>
+__global__ void pointwise_kernel(T* __restrict__ a, const T* __restrict__ b, int b_stride, int cols, size_t total,
+                                 int op, float ca, float cb) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const float av = to_f32(a[idx]);
+    float bv = 0.f;
+    if (b) bv = to_f32(b[(idx / cols) * (size_t)b_stride + idx % cols]);
+    float r;
+    if (op == 0) r = av / (1.f + expf(-bv));
+    else if (op == 1) r = ca * av + cb * bv;
+    else r = tanhf(av);
+    a[idx] = from_f32<T>(r);
+}
+
+IB_EXPORT int ib_pointwise(void* a, const void* b, int b_stride, int act_dtype, int rows, int cols, int op, float ca,
+                           float cb, void* stream) {
+    if (rows <= 0 || cols <= 0) return IB_OK;
+    if (!a || (op != 2 && !b) || op < 0 || op > 2) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)rows * cols;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(pointwise_kernel<float>, dim3(grid), dim3(256), 0, s, (float*)a, (const float*)b, b_stride,
+                           cols, total, op, ca, cb);
+    else if (act_dtype == 1)
+        le = launch_kernel(pointwise_kernel<bf16>, dim3(grid), dim3(256), 0, s, (bf16*)a, (const bf16*)b, b_stride,
+                           cols, total, op, ca, cb);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}

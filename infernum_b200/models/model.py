@@ -55,7 +55,7 @@ class Model:
         specs: Dict[str, WeightSpec] = {}
         for part in self._all_parts():
             for name, ws in part.weight_specs().items():
-                if name in specs and specs[name].shape != ws.shape:
+                if name in specs and tuple(specs[name].shape) != tuple(ws.shape):
                     raise ConfigError(f"tensor {name!r} is declared twice with different shapes")
                 specs[name] = ws
         return specs

@@ -16,20 +16,21 @@ from . import core
 
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     out: torch.Tensor, ctx, tables: torch.Tensor, n_heads: int, scale: float,
-                    window: int, rt) -> None:
+                    window: int, rt, sink=None) -> None:
     """Attention of every row of the step over its request's pages.
 
     ``q`` holds the (already position-encoded) queries in its first
     ``n_heads * head_dim`` columns; keys and values of the step's own tokens
-    are already in the pools."""
+    are already in the pools.  ``sink`` (float32 [n_heads]): a logit per head
+    whose exponential is added to the softmax's denominator."""
     impl = rt.options.get("attention", "auto")
     if q.dtype == torch.bfloat16 and impl != "plain":
         from . import attention_fast
 
-        if attention_fast.run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt):
+        if attention_fast.run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=sink):
             return
     core.attention_plain(q, k_pool, v_pool, out, ctx.positions, ctx.row_entry, tables, n_heads,
-                         scale, window, rt.err)
+                         scale, window, rt.err, sink=sink)
 
 
 def latent_attention(q_abs: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, kv_rank: int, ctx,

@@ -152,9 +152,9 @@ def _step_plan(ctx, G: int, nkv: int, tc_ok: bool, rt) -> dict:
     return plan
 
 
-def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt) -> bool:
+def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=None) -> bool:
     num_pages, nkv, page_size, hd = k_pool.shape
-    if not supported(hd):
+    if not supported(hd) or sink is not None:
         return False
     core.require_cuda(q, k_pool, v_pool, out, tables)
     if n_heads % nkv:

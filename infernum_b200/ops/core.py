@@ -17,7 +17,7 @@ from ..csrc.build import load_module
 from ..errors import KernelError
 
 CORE_SOURCES = ["elementwise.cu", "attention_plain.cu", "gemm_plain.cu", "sampling.cu", "layernorm.cu",
-                "embed_hashed.cu", "latent.cu", "moe.cu"]
+                "embed_hashed.cu", "latent.cu", "moe.cu", "hyper.cu", "recurrent.cu"]
 
 _c_int = ctypes.c_int
 _c_float = ctypes.c_float
@@ -82,7 +82,7 @@ def core_lib() -> ctypes.CDLL:
         lib.ib_feed_tokens.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p,
                                        _c_void_p]
         lib.ib_attention_plain_ex.argtypes = lib.ib_attention_plain.argtypes[:19] + [_c_int, _c_int, _c_int, _c_int,
-                                                                                  _c_void_p, _c_void_p]
+                                                                                  _c_void_p, _c_void_p, _c_void_p]
         lib.ib_gemm_plain_batched.argtypes = [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_ll,
                                               _c_void_p, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int,
                                               _c_void_p]
@@ -104,6 +104,27 @@ def core_lib() -> ctypes.CDLL:
         lib.ib_router_logits.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
                                          _c_int, _c_void_p]
         lib.ib_router_logits.restype = _c_int
+        lib.ib_hc_norm.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                   _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p]
+        lib.ib_embed_sinusoid.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
+                                          _c_int, _c_int, _c_void_p, _c_void_p]
+        lib.ib_scale_inplace.argtypes = [_c_void_p, _c_ll, _c_float, _c_void_p]
+        lib.ib_token_shift.argtypes = [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p,
+                                       _c_void_p, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_causal_conv_silu.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p,
+                                            _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_head_norm_gate.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
+                                          _c_int, _c_float, _c_void_p]
+        lib.ib_gated_group_norm.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
+                                            _c_int, _c_float, _c_void_p]
+        lib.ib_qk_norm_append.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p,
+                                          _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                          _c_int, _c_int, _c_void_p, _c_void_p]
+        lib.ib_pointwise.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float,
+                                     _c_void_p]
+        for fn in ("ib_hc_norm", "ib_embed_sinusoid", "ib_scale_inplace", "ib_token_shift", "ib_causal_conv_silu",
+                   "ib_head_norm_gate", "ib_gated_group_norm", "ib_qk_norm_append", "ib_pointwise"):
+            getattr(lib, fn).restype = _c_int
         for fn in ("ib_attention_plain_ex", "ib_gemm_plain_batched", "ib_gated_act", "ib_scale_add_norm",
                    "ib_softcap", "ib_embed_hashed", "ib_latent_prepare", "ib_latent_q_rotate", "ib_moe_route"):
             getattr(lib, fn).restype = _c_int
@@ -398,12 +419,14 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: Optional[int] = No
 def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     out: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor,
                     block_tables: torch.Tensor, n_heads: int, scale: float, window: int,
-                    err: torch.Tensor) -> None:
+                    err: torch.Tensor, sink: Optional[torch.Tensor] = None) -> None:
     """Causal attention of each row over its request's pages (32-bit arithmetic).
 
     ``q`` is [N, >= n_heads*hd] (a view into the qkv rows is fine), ``out`` is
-    [N, n_heads*hd]; pools are [pages, kv_heads, page_size, hd]."""
-    require_cuda(q, k_pool, v_pool, out, positions, row_entry, block_tables, err)
+    [N, n_heads*hd]; pools are [pages, kv_heads, page_size, hd].  ``sink``
+    (float32 [n_heads]): a logit per head that is added to the softmax's
+    denominator as exp(sink), with no key and no value behind it."""
+    require_cuda(q, k_pool, v_pool, out, positions, row_entry, block_tables, err, sink)
     _int32(positions, "positions")
     _int32(row_entry, "row_entry")
     _int32(block_tables, "block_tables")
@@ -416,6 +439,16 @@ def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         raise KernelError("attention_plain: q, pools and out must share a dtype")
     if n_heads % nkv:
         raise KernelError(f"attention: {n_heads} heads are not a multiple of {nkv} kv heads")
+    if sink is not None:
+        if sink.dtype != torch.float32 or sink.shape != (n_heads,) or not sink.is_contiguous():
+            raise KernelError(f"attention_plain: sink must be contiguous float32 [{n_heads}]")
+        check(core_lib().ib_attention_plain_ex(q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
+                                               out.data_ptr(), out.stride(0), dtype_code(q.dtype),
+                                               positions.data_ptr(), row_entry.data_ptr(), block_tables.data_ptr(),
+                                               block_tables.shape[1], N, n_heads, nkv, hd, page_size, num_pages,
+                                               int(window), float(scale), hd, hd, hd, hd, sink.data_ptr(),
+                                               err.data_ptr(), stream_ptr(q)), "attention_plain")
+        return
     check(core_lib().ib_attention_plain(q.data_ptr(), q.stride(0), k_pool.data_ptr(),
                                         v_pool.data_ptr(), out.data_ptr(), out.stride(0),
                                         dtype_code(q.dtype), positions.data_ptr(),
@@ -697,7 +730,7 @@ def attention_latent_plain(q_abs: torch.Tensor, pool: torch.Tensor, out: torch.T
                                            positions.data_ptr(), row_entry.data_ptr(), block_tables.data_ptr(),
                                            block_tables.shape[1], N, heads, 1, width, page_size, num_pages,
                                            int(window), float(scale), int(kv_rank), width, q_abs.stride(1),
-                                           out.stride(1), err.data_ptr(), stream_ptr(q_abs)),
+                                           out.stride(1), None, err.data_ptr(), stream_ptr(q_abs)),
           "attention_latent_plain")
 
 
@@ -747,3 +780,196 @@ def router_logits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     check(core_lib().ib_router_logits(x.data_ptr(), dtype_code(x.dtype), x.stride(0), w.data_ptr(),
                                       dtype_code(w.dtype), w.stride(0), out.data_ptr(), N, E, K, stream_ptr(out)),
           "router_logits")
+
+
+# ---------------------------------------------------------------------------
+# Several residual streams per token, a sinusoidal position vector on the
+# embedding, recurrent mixers (token shift, causal convolution, the norms and
+# gates behind their scans) and attention with normed queries and keys.
+# ---------------------------------------------------------------------------
+def _f32_vec(t: Optional[torch.Tensor], n: int, name: str) -> None:
+    if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+        raise KernelError(f"{name} must be contiguous float32 with {n} values")
+
+
+def hc_norm(x: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+            out_coef: Optional[torch.Tensor], read: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+            bias: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor], centred: bool = True,
+            row_idx: Optional[torch.Tensor] = None) -> None:
+    """Streams ``x`` [N, S, H] (float32): with ``y`` [N, H] the write of a
+    sub-layer, ``x_t <- sum_s mix[s, t] x_s + out_coef[t] y``; with ``out`` the
+    read ``u = sum_s read[s] x_s`` (``read`` None: the plain sum) and its norm
+    with ``weight`` and ``bias`` into ``out``.  One pass, 32-bit.  With
+    ``row_idx`` only those rows are read, ``out`` is compact and nothing is
+    written back."""
+    require_cuda(x, y, mix, out_coef, read, weight, bias, out, row_idx)
+    if x.dim() != 3 or x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("hc_norm: the streams must be contiguous float32 [N, S, H]")
+    N, S, H = x.shape
+    _int32(row_idx, "row_idx")
+    n_out = N if row_idx is None else row_idx.numel()
+    _f32_vec(mix, S * S, "hc_norm: mix")
+    _f32_vec(out_coef, S, "hc_norm: out_coef")
+    _f32_vec(read, S, "hc_norm: read")
+    if y is not None and (y.shape != (N, H) or not y.is_contiguous() or mix is None or out_coef is None):
+        raise KernelError("hc_norm: y must be contiguous [N, H] and comes with mix and out_coef")
+    if out is not None and (out.shape != (n_out, H) or not out.is_contiguous() or weight is None
+                            or weight.shape != (H,) or not weight.is_contiguous()
+                            or (bias is not None and (bias.shape != (H,) or bias.dtype != weight.dtype
+                                                      or not bias.is_contiguous()))):
+        raise KernelError(f"hc_norm: out must be contiguous [{n_out}, {H}], weight and bias [{H}] of one dtype")
+    if y is not None and out is not None and y.dtype != out.dtype:
+        raise KernelError("hc_norm: y and out share the activation dtype")
+    act = out.dtype if out is not None else (y.dtype if y is not None else torch.float32)
+    check(core_lib().ib_hc_norm(x.data_ptr(), _ptr(y), _ptr(mix), _ptr(out_coef), _ptr(read), _ptr(weight),
+                                _ptr(bias), dtype_code(weight.dtype) if weight is not None else 0, _ptr(out),
+                                dtype_code(act), _ptr(row_idx), n_out, S, H, float(eps), 1 if centred else 0,
+                                stream_ptr(x)), "hc_norm")
+
+
+def embed_sinusoid(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, inv_freq: torch.Tensor,
+                   out: torch.Tensor, err: torch.Tensor) -> None:
+    """out[t, s, c] = table[ids[t], c] + (sin | cos)(positions[t] * inv_freq[c // 2])
+    for every stream s (even c: sine, odd c: cosine); ``out`` float32 [N, S, H]."""
+    require_cuda(ids, positions, table, inv_freq, out, err)
+    _int32(ids, "ids")
+    _int32(positions, "positions")
+    n = ids.numel()
+    V, H = table.shape
+    if out.dim() != 3 or out.dtype != torch.float32 or out.shape[0] != n or out.shape[2] != H or not out.is_contiguous():
+        raise KernelError(f"embed_sinusoid: out must be contiguous float32 [{n}, S, {H}]")
+    _f32_vec(inv_freq, (H + 1) // 2, "embed_sinusoid: inv_freq")
+    if not table.is_contiguous():
+        raise KernelError("embed_sinusoid: table must be contiguous")
+    check(core_lib().ib_embed_sinusoid(ids.data_ptr(), positions.data_ptr(), table.data_ptr(), dtype_code(table.dtype),
+                                       inv_freq.data_ptr(), out.data_ptr(), n, H, V, out.shape[1], err.data_ptr(),
+                                       stream_ptr(out)), "embed_sinusoid")
+
+
+def scale_inplace(x: torch.Tensor, scale: float) -> None:
+    """x <- x * scale (float32, in place)."""
+    require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_inplace: x must be contiguous float32")
+    check(core_lib().ib_scale_inplace(x.data_ptr(), x.numel(), float(scale), stream_ptr(x)), "scale_inplace")
+
+
+def _state_view(state: torch.Tensor, offset: int):
+    """(pointer to the state's element ``offset`` of slot 0, floats between slots)."""
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous():
+        raise KernelError("a recurrent state must be contiguous float32 [slots, floats]")
+    return state.data_ptr() + 4 * int(offset), state.stride(0)
+
+
+def token_shift(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, state_offset: int, ctx,
+                out: torch.Tensor) -> None:
+    """out[j, t] = x[t] + (x[t-1] - x[t]) * mu[j]; the row before an entry's first
+    is the request's state (``state[slot, offset : offset + D]``), which takes the
+    entry's last row.  ``mu`` float32 [M, D], ``out`` [M, N, D]."""
+    require_cuda(x, mu, state, out)
+    N, D = x.shape
+    M = mu.shape[0]
+    _f32_vec(mu, M * D, "token_shift: mu")
+    if not x.is_contiguous() or out.shape != (M, N, D) or out.dtype != x.dtype or not out.is_contiguous():
+        raise KernelError("token_shift: x [N, D] and out [M, N, D] must be contiguous, one dtype")
+    ptr, stride = _state_view(state, state_offset)
+    check(core_lib().ib_token_shift(x.data_ptr(), dtype_code(x.dtype), mu.data_ptr(), ptr, stride,
+                                    ctx.row_entry.data_ptr(), ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(),
+                                    out.data_ptr(), N, D, M, stream_ptr(x)), "token_shift")
+
+
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                     state_offset: int, ctx, out: torch.Tensor) -> None:
+    """Per channel: out[t] = silu(bias + sum_j weight[:, j] x[t - (taps-1-j)]) inside
+    each request; inputs before the step come from ``state[slot, offset:]``
+    ([taps-1, C], the newest last), which is brought up to date.  ``x`` [N, C] may
+    be a view of wider rows; ``weight`` float32 [C, taps]."""
+    require_cuda(x, weight, bias, state, out)
+    N, C = x.shape
+    taps = weight.shape[1]
+    _f32_vec(weight, C * taps, "causal_conv_silu: weight")
+    _f32_vec(bias, C, "causal_conv_silu: bias")
+    if x.stride(1) != 1 or out.shape != (N, C) or out.dtype != x.dtype or not out.is_contiguous():
+        raise KernelError("causal_conv_silu: x [N, C] with unit inner stride, out contiguous [N, C] of x's dtype")
+    ptr, stride = _state_view(state, state_offset)
+    check(core_lib().ib_causal_conv_silu(x.data_ptr(), x.stride(0), dtype_code(x.dtype), weight.data_ptr(), _ptr(bias),
+                                         ptr, stride, ctx.row_entry.data_ptr(), ctx.cu_rows.data_ptr(),
+                                         ctx.slot_ids.data_ptr(), out.data_ptr(), N, ctx.n_entries, C, taps,
+                                         stream_ptr(x)), "causal_conv_silu")
+
+
+def head_norm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, heads: int, eps: float,
+                   out: torch.Tensor) -> None:
+    """out = o / rms_head(o) * weight * silu(gate): ``o`` float32 [N, heads * K], the
+    root mean square taken over each head's K values."""
+    require_cuda(o, gate, weight, out)
+    N, HK = o.shape
+    if o.dtype != torch.float32 or not o.is_contiguous() or HK % heads or out.shape != (N, HK) \
+            or not out.is_contiguous():
+        raise KernelError("head_norm_gate: o contiguous float32 [N, heads * K], out contiguous of the same shape")
+    _f32_vec(weight, HK, "head_norm_gate: weight")
+    if gate is not None and (gate.shape != (N, HK) or gate.stride(1) != 1 or gate.dtype != out.dtype):
+        raise KernelError("head_norm_gate: gate [N, heads * K] of out's dtype with unit inner stride")
+    check(core_lib().ib_head_norm_gate(o.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                       dtype_code(out.dtype), weight.data_ptr(), out.data_ptr(), N, heads,
+                                       HK // heads, float(eps), stream_ptr(o)), "head_norm_gate")
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, groups: int, eps: float,
+                     out: torch.Tensor) -> None:
+    """v = y * silu(z); out = v / rms_group(v) * weight, the root mean square over
+    each of ``groups`` equal parts of a row.  ``y`` float32 [N, inner]; ``z`` may
+    be a view of wider rows."""
+    require_cuda(y, z, weight, out)
+    N, inner = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or inner % groups or out.shape != (N, inner) \
+            or not out.is_contiguous() or z.shape != (N, inner) or z.stride(1) != 1 or z.dtype != out.dtype:
+        raise KernelError("gated_group_norm: y float32 [N, inner], z and out [N, inner] of the activation dtype")
+    _f32_vec(weight, inner, "gated_group_norm: weight")
+    check(core_lib().ib_gated_group_norm(y.data_ptr(), z.data_ptr(), z.stride(0), dtype_code(out.dtype),
+                                         weight.data_ptr(), out.data_ptr(), N, inner, int(groups), float(eps),
+                                         stream_ptr(y)), "gated_group_norm")
+
+
+def qk_norm_append(x: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                   n_heads: int, n_kv_heads: int, head_dim: int, v_offset: int, positions: torch.Tensor,
+                   row_entry: torch.Tensor, block_tables: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   err: torch.Tensor) -> None:
+    """Rows of ``x`` hold ``n_heads`` query heads and then ``n_kv_heads`` key heads.
+    Queries are RMS-normed per head in place (times ``q_weight`` [head_dim]); each
+    key goes normed (times ``k_weight``) to its place in ``k_pool``, and the value
+    pool gets the value head ``v_offset`` elements into the row, or - ``v_offset``
+    negative - the key as it was projected."""
+    require_cuda(x, q_weight, k_weight, positions, row_entry, block_tables, k_pool, v_pool, err)
+    _int32(positions, "positions")
+    _int32(row_entry, "row_entry")
+    _int32(block_tables, "block_tables")
+    _f32_vec(q_weight, head_dim, "qk_norm_append: q_weight")
+    _f32_vec(k_weight, head_dim, "qk_norm_append: k_weight")
+    if x.dim() != 2 or x.stride(1) != 1 or x.shape[1] < (n_heads + n_kv_heads) * head_dim:
+        raise KernelError("qk_norm_append: x rows must hold the query and key heads with unit inner stride")
+    num_pages, nkv_pool, page_size, hd_pool = k_pool.shape
+    if k_pool.shape != v_pool.shape or nkv_pool != n_kv_heads or hd_pool != head_dim or k_pool.dtype != x.dtype \
+            or v_pool.dtype != x.dtype or not k_pool.is_contiguous() or not v_pool.is_contiguous():
+        raise KernelError("qk_norm_append: pools must be contiguous [pages, kv_heads, page_size, head_dim] of x's dtype")
+    check(core_lib().ib_qk_norm_append(x.data_ptr(), x.stride(0), dtype_code(x.dtype), _ptr(q_weight), _ptr(k_weight),
+                                       float(eps), positions.data_ptr(), row_entry.data_ptr(), block_tables.data_ptr(),
+                                       block_tables.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), x.shape[0],
+                                       n_heads, n_kv_heads, head_dim, int(v_offset), page_size, num_pages,
+                                       err.data_ptr(), stream_ptr(x)), "qk_norm_append")
+
+
+_POINTWISE = {"sigmoid_gate": 0, "axpby": 1, "tanh": 2}
+
+
+def pointwise(a: torch.Tensor, b: Optional[torch.Tensor], op: str, ca: float = 1.0, cb: float = 1.0) -> None:
+    """In place on ``a`` [N, C] (contiguous): ``sigmoid_gate`` a * sigmoid(b);
+    ``axpby`` ca * a + cb * b; ``tanh`` tanh(a).  ``b`` may be a view of wider rows."""
+    require_cuda(a, b)
+    if a.dim() != 2 or not a.is_contiguous() or op not in _POINTWISE:
+        raise KernelError("pointwise: a must be contiguous [N, C]; ops: " + ", ".join(sorted(_POINTWISE)))
+    if b is not None and (b.shape != a.shape or b.stride(1) != 1 or b.dtype != a.dtype):
+        raise KernelError("pointwise: b must have a's shape and dtype with unit inner stride")
+    check(core_lib().ib_pointwise(a.data_ptr(), _ptr(b), b.stride(0) if b is not None else 0, dtype_code(a.dtype),
+                                  a.shape[0], a.shape[1], _POINTWISE[op], float(ca), float(cb), stream_ptr(a)),
+          "pointwise_" + op)

@@ -1,0 +1,127 @@
+"""The scans of recurrent mixers (``scan.cu``): one compiled module per number
+of rows of the per-head state matrix, built when a model first needs it.
+
+``wkv_scan`` and ``ssd_scan`` walk every entry's rows in order from the state in
+the request's slot and leave the new state there; what they need to know about
+the step (entries, slots) they read from the step's device tensors, so a
+recorded step replays them for other requests.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Dict
+
+import torch
+
+from ..csrc.build import load_module
+from ..errors import KernelError
+from . import core
+
+_c_int, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_void_p, ctypes.c_longlong
+_libs: Dict[int, ctypes.CDLL] = {}
+MAX_ROWS = 512
+SM_COUNT_FALLBACK = 148
+
+
+def lib_for(rows: int) -> ctypes.CDLL:
+    lib = _libs.get(rows)
+    if lib is None:
+        if not 1 <= rows <= MAX_ROWS:
+            raise KernelError(f"recurrent scan: a state of {rows} rows per head is outside 1..{MAX_ROWS}")
+        lib = load_module(f"scan_r{rows}", ["scan.cu"], [f"-DIB_ROWS={rows}"])
+        lib.ib_wkv_scan.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                    _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                                    _c_void_p]
+        lib.ib_ssd_scan.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                    _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                                    _c_int, _c_void_p]
+        for fn in ("ib_wkv_scan", "ib_ssd_scan", "ib_scan_rows", "ib_scan_split"):
+            getattr(lib, fn).restype = _c_int
+        if lib.ib_scan_rows() != rows:
+            raise KernelError(f"scan module for {rows} state rows was built for another size")
+        _libs[rows] = lib
+    return lib
+
+
+def choose_col_slices(n_entries: int, heads: int, cols: int, split: int, sm_count: int) -> int:
+    """Into how many CTAs the columns of a head's state are cut.  A CTA walks its
+    entry's tokens one after the other, so the scan's time is the longest entry's
+    whatever the grid; slices shorten it by giving every CTA fewer columns, while
+    the grid still fits the SMs in one round and a CTA keeps at least two warps.
+    A CTA takes at most 512 threads.  The result does not change any number: a
+    column's arithmetic is the same in every slicing."""
+    slices = 1
+    while cols % (slices * 2) == 0 and (
+            (cols // slices) * split > 512
+            or (n_entries * heads * slices * 2 <= 2 * sm_count and (cols // (slices * 2)) * split >= 64)):
+        slices *= 2
+    if (cols // slices) * split > 512:
+        # (no power of two cuts it small enough: take the smallest divisor that does)
+        for s in range(slices + 1, cols + 1):
+            if cols % s == 0 and (cols // s) * split <= 512:
+                return s
+    return slices
+
+
+def _state_ptr(state: torch.Tensor, offset: int):
+    if state.dtype != torch.float32 or state.dim() != 2 or not state.is_contiguous():
+        raise KernelError("a recurrent state must be contiguous float32 [slots, floats]")
+    return state.data_ptr() + 4 * int(offset), state.stride(0)
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, u: torch.Tensor,
+             state: torch.Tensor, state_offset: int, ctx, out: torch.Tensor, heads: int, rt) -> None:
+    """Per head, with S [K, K] from ``state[slot, offset:]``:
+    ``o_t = (S + diag(u) k_t v_t^T)^T r_t``, then ``S <- diag(w_t) S + k_t v_t^T``
+    with ``w_t = exp(-exp(z_t + w0))``.  ``r, k, v`` [N, heads * K] (activation
+    dtype, one row stride), ``z`` float32 [N, heads * K], ``out`` float32."""
+    core.require_cuda(r, k, v, z, w0, u, state, out)
+    N, HK = r.shape
+    K = HK // heads
+    if HK % heads or k.shape != r.shape or v.shape != r.shape or not (r.dtype == k.dtype == v.dtype) \
+            or r.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or not (r.stride(0) == k.stride(0) == v.stride(0)):
+        raise KernelError("wkv_scan: r, k, v must be [N, heads * K] of one dtype and one row stride")
+    if z.shape != (N, HK) or z.dtype != torch.float32 or not z.is_contiguous() \
+            or out.shape != (N, HK) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("wkv_scan: z and out must be contiguous float32 [N, heads * K]")
+    for t, name in ((w0, "w0"), (u, "u")):
+        if t.dtype != torch.float32 or t.numel() != HK or not t.is_contiguous():
+            raise KernelError(f"wkv_scan: {name} must be contiguous float32 with {HK} values")
+    lib = lib_for(K)
+    ptr, stride = _state_ptr(state, state_offset)
+    sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
+    slices = choose_col_slices(ctx.n_entries, heads, K, lib.ib_scan_split(), sm)
+    core.check(lib.ib_wkv_scan(r.data_ptr(), k.data_ptr(), v.data_ptr(), r.stride(0), core.dtype_code(r.dtype),
+                               z.data_ptr(), w0.data_ptr(), u.data_ptr(), ptr, stride, ctx.cu_rows.data_ptr(),
+                               ctx.slot_ids.data_ptr(), out.data_ptr(), ctx.n_entries, heads, K, slices,
+                               core.stream_ptr(r)), "wkv_scan")
+
+
+def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, state_offset: int, ctx, out: torch.Tensor, heads: int, groups: int,
+             state_rows: int, vdim: int, rt) -> None:
+    """Per head, with S [state_rows, vdim] from ``state[slot, offset:]``:
+    ``S <- exp(-exp(a_log) dt) S + dt B_t x_t^T``, ``y_t = S^T C_t + d_skip x_t``,
+    ``dt = softplus(dt_raw + dt_bias)``.  ``xbc`` [N, heads*vdim + 2*groups*state_rows]
+    holds x, B and C side by side; ``dt`` [N, heads] may be a view of wider rows;
+    ``out`` float32 [N, heads * vdim]."""
+    core.require_cuda(xbc, dt, dt_bias, a_log, d_skip, state, out)
+    N = xbc.shape[0]
+    inner = heads * vdim
+    if xbc.shape[1] != inner + 2 * groups * state_rows or xbc.stride(1) != 1 or dt.shape != (N, heads) \
+            or dt.stride(1) != 1 or dt.dtype != xbc.dtype or heads % groups:
+        raise KernelError("ssd_scan: xbc [N, inner + 2 groups state] and dt [N, heads] of one dtype do not fit")
+    if out.shape != (N, inner) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("ssd_scan: out must be contiguous float32 [N, heads * vdim]")
+    for t, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        if t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous():
+            raise KernelError(f"ssd_scan: {name} must be contiguous float32 [{heads}]")
+    lib = lib_for(state_rows)
+    ptr, stride = _state_ptr(state, state_offset)
+    sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
+    slices = choose_col_slices(ctx.n_entries, heads, vdim, lib.ib_scan_split(), sm)
+    core.check(lib.ib_ssd_scan(xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0), core.dtype_code(xbc.dtype),
+                               dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), ptr, stride,
+                               ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(), out.data_ptr(), ctx.n_entries, heads,
+                               groups, vdim, slices, core.stream_ptr(xbc)), "ssd_scan")

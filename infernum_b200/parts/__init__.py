@@ -6,4 +6,5 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
                    PartSpec, PositionEncoding, ResidualStream, Runtime, ScheduleItem, StateSpec,
                    WeightSpec, build_layer, register_block, register_feed_forward, register_mixer,
                    register_norm, register_position_encoding)
-from . import attention, block, embedding, latent_attention, mlp, moe, norm, rope  # noqa: F401  (registration)
+from . import (attention, block, embedding, latent_attention, mlp, moe, norm, parallel, recurrent,  # noqa: F401  (registration)
+               rope)

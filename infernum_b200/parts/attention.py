@@ -17,6 +17,18 @@ Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
 ``prefix`` (checkpoint prefix, e.g. "model.layers.0.self_attn."),
 ``kv_shared`` (True: the layer has no k/v projection and reads the cache of
 another run named by the schedule).
+
+Options beyond the Llama layer, all off by default:
+``names`` (the tensors' names behind the prefix: ``q``, ``k``, ``v``, ``o``);
+``qk_norm`` ({"q": name, "k": name, "eps": e}): queries and keys are divided by
+their root mean square per head and multiplied by a weight of ``head_dim``
+values that all heads share, before the scores;
+``value_from_key`` (True: there is no value projection; a token's value is its
+key as projected, before any norm);
+``sink`` (a tensor name: one learned logit per head whose exponential is added
+to the softmax's denominator; it has no key and no value and is not scaled);
+``gate`` (a tensor name: the concatenated heads are multiplied by
+``sigmoid(W_gate x)`` before the output projection).
 """
 
 from __future__ import annotations
@@ -54,8 +66,24 @@ class Attention(Mixer):
         self.position = None
         if pos:
             self.position = POSITION_ENCODINGS.get(pos["kind"])(pos.get("params", {}), rt)
+        names = params.get("names") or {}
+        self.names = {k: self.prefix + names.get(k, f"{k}_proj.weight") for k in ("q", "k", "v", "o")}
+        qk_norm = params.get("qk_norm")
+        self.qk_norm = None
+        if qk_norm:
+            self.qk_norm = {"q": self.prefix + qk_norm["q"], "k": self.prefix + qk_norm["k"],
+                            "eps": float(qk_norm["eps"])}
+        self.value_from_key = bool(params.get("value_from_key", False))
+        self.sink_name = self.prefix + params["sink"] if params.get("sink") else None
+        self.gate_name = self.prefix + params["gate"] if params.get("gate") else None
+        if (self.qk_norm or self.value_from_key) and self.position is not None:
+            raise ConfigError("attention: normed queries and keys, or values taken from keys, "
+                              "are not combined with a position encoding")
+        if (self.qk_norm or self.value_from_key) and self.kv_shared:
+            raise ConfigError("attention: normed keys or values taken from keys need a cache of the layer's own")
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
+        self.q_norm_w = self.k_norm_w = self.sink = None
 
     # ---- declarations -----------------------------------------------------
     def cache_spec(self) -> Optional[PagedCacheSpec]:
@@ -64,30 +92,63 @@ class Attention(Mixer):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         qd, kvd = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
         specs = {
-            self.prefix + "q_proj.weight": WeightSpec((qd, self.hidden_size)),
-            self.prefix + "o_proj.weight": WeightSpec((self.hidden_size, qd)),
+            self.names["q"]: WeightSpec((qd, self.hidden_size)),
+            self.names["o"]: WeightSpec((self.hidden_size, qd)),
         }
         if not self.kv_shared:
-            specs[self.prefix + "k_proj.weight"] = WeightSpec((kvd, self.hidden_size))
-            specs[self.prefix + "v_proj.weight"] = WeightSpec((kvd, self.hidden_size))
+            specs[self.names["k"]] = WeightSpec((kvd, self.hidden_size))
+            if not self.value_from_key:
+                specs[self.names["v"]] = WeightSpec((kvd, self.hidden_size))
+        if self.qk_norm:
+            specs[self.qk_norm["q"]] = WeightSpec((self.head_dim,), init="norm")
+            specs[self.qk_norm["k"]] = WeightSpec((self.head_dim,), init="norm")
+        if self.sink_name:
+            specs[self.sink_name] = WeightSpec((self.num_heads,), init="normal", std=1.0)
+        if self.gate_name:
+            specs[self.gate_name] = WeightSpec((qd, self.hidden_size))
         return specs
 
     def bind(self, weights) -> None:
-        names = ["q_proj.weight"] + ([] if self.kv_shared else ["k_proj.weight", "v_proj.weight"])
-        mats = [weights[self.prefix + n] for n in names]
+        keys = ["q"] + ([] if self.kv_shared else (["k"] if self.value_from_key else ["k", "v"]))
+        mats = [weights[self.names[n]] for n in keys]
+        if self.gate_name:
+            mats.append(weights[self.gate_name])  # the gate rides in the same product, behind q, k (and v)
         if len({m.dtype for m in mats}) != 1:
             raise ConfigError(f"{self.prefix}: q/k/v projections are stored in different dtypes")
         self.qkv = Linear(torch.cat(mats, dim=0) if len(mats) > 1 else mats[0], self.rt)
-        self.o = Linear(weights[self.prefix + "o_proj.weight"], self.rt)
+        self.o = Linear(weights[self.names["o"]], self.rt)
+        if self.qk_norm:
+            self.q_norm_w = weights[self.qk_norm["q"]].to(torch.float32).contiguous()
+            self.k_norm_w = weights[self.qk_norm["k"]].to(torch.float32).contiguous()
+        if self.sink_name:
+            self.sink = weights[self.sink_name].to(torch.float32).contiguous()
 
     def weight_bytes(self) -> int:
         return self.qkv.nbytes + self.o.nbytes
 
     # ---- the step -----------------------------------------------------------
-    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    def project(self, x: torch.Tensor) -> torch.Tensor:
+        """The fused product: rows of q | k | (v) | (gate)."""
+        return self.qkv(x)
+
+    @property
+    def projected_rows(self) -> int:
+        return self.qkv.out_features
+
+    def forward(self, x: torch.Tensor, ctx, cache, projected: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``projected``: the fused product when the caller has already made it
+        (as part of a wider one); a view of wider rows is fine."""
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = self.qkv(x)  # [N, (nh + 2 nkv) hd], or [N, nh hd] when the cache is shared
+        qkv = projected if projected is not None else self.qkv(x)  # [N, (nh + 2 nkv) hd (+ gate)], or [N, nh hd] when the cache is shared
         tables = ctx.block_tables[cache.group]
+        if self.qk_norm or self.value_from_key:
+            if not cache.owner:
+                raise ConfigError("attention with normed keys must own its cache")
+            v_off = -1 if self.value_from_key else (nh + nkv) * hd
+            core.qk_norm_append(qkv, self.q_norm_w, self.k_norm_w, self.qk_norm["eps"] if self.qk_norm else 1e-6,
+                                nh, nkv, hd, v_off, ctx.positions, ctx.row_entry, tables, cache.k_pool, cache.v_pool,
+                                self.rt.err)
+            return self._attend(qkv, ctx, cache, tables)
         writes = cache.owner and not self.kv_shared
         if self.kv_shared and cache.owner:
             raise ConfigError("a kv_shared attention layer must be scheduled with cache_of")
@@ -103,7 +164,14 @@ class Attention(Mixer):
             nh, nkv if writes else 0, hd,
             ctx.row_entry if writes else None, tables if writes else None,
             cache.k_pool if writes else None, cache.v_pool if writes else None, self.rt.err)
+        return self._attend(qkv, ctx, cache, tables)
+
+    def _attend(self, qkv: torch.Tensor, ctx, cache, tables) -> torch.Tensor:
+        nh, hd = self.num_heads, self.head_dim
         out = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
         attn_ops.paged_attention(qkv, cache.k_pool, cache.v_pool, out, ctx, tables, nh,
-                                 self.scale, self.window, self.rt)
+                                 self.scale, self.window, self.rt, sink=self.sink)
+        if self.gate_name:
+            g0 = self.qkv.out_features - nh * hd
+            core.pointwise(out, qkv[:, g0: g0 + nh * hd], "sigmoid_gate")
         return self.o(out)

@@ -47,6 +47,23 @@ class WeightSpec:
     # True: the checkpoint may leave the tensor out; the part is then bound without
     # it and must cope (the random-weights mode always draws it)
     optional: bool = False
+    # A dimension of -1 in ``shape`` is taken from the checkpoint (a size that no
+    # configuration key names, the rank of a low-rank pair say); the random-weights
+    # mode then draws ``draw_shape``.
+    draw_shape: Optional[Tuple[int, ...]] = None
+
+    def matches(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w < 0 or w == g for w, g in zip(self.shape, shape))
+
+    @property
+    def concrete_shape(self) -> Tuple[int, ...]:
+        """The shape to draw: ``shape``, or ``draw_shape`` when a dimension is free."""
+        if any(d < 0 for d in self.shape):
+            if self.draw_shape is None:
+                raise ConfigError(f"a tensor of shape {list(self.shape)} has a free dimension and no size to draw")
+            return tuple(self.draw_shape)
+        return tuple(self.shape)
 
 
 @dataclass(frozen=True)
@@ -278,25 +295,40 @@ class ResidualStream:
     ``flush``) adds to it.  Keeping the sum in 32-bit and fusing the add into
     the norm kernel saves one pass over the rows per sub-layer."""
 
-    def __init__(self, residual: torch.Tensor, act: Optional[torch.Tensor] = None):
+    def __init__(self, residual: torch.Tensor, act: Optional[torch.Tensor] = None, streams: int = 1):
         self.residual = residual
         self.pending: Optional[torch.Tensor] = None
+        # More than one stream per token (hyper-connections): ``residual`` is
+        # [N, streams, hidden], and a pending delta comes with the coefficients that
+        # write it into the streams: ``pending_write = (mix [S, S], out [S])`` for
+        # ``x_t <- sum_s mix[s, t] x_s + out[t] * delta``.
+        self.streams = int(streams)
+        self.pending_write = None
         # The residual rounded to the activation dtype, for arrangements whose
         # sub-layers read the stream itself (norm after the sum); valid while
         # nothing is pending.  In a float32 engine it is the residual.
         self.act = act
 
-    def push(self, delta: torch.Tensor) -> None:
+    def push(self, delta: torch.Tensor, write=None) -> None:
         if self.pending is not None:
             self.flush()
+        if (write is None) != (self.residual.dim() == 2):
+            raise ConfigError("a stream of several copies takes a delta with its write coefficients, "
+                              "a single one without")
         self.pending = delta
+        self.pending_write = write
 
     def flush(self) -> None:
         if self.pending is not None:
             from ..ops import core
 
-            core.residual_add(self.residual, self.pending)
+            if self.pending_write is not None:
+                mix, out_coef = self.pending_write
+                core.hc_norm(self.residual, self.pending, mix, out_coef, None, None, None, 1.0, None)
+            else:
+                core.residual_add(self.residual, self.pending)
             self.pending = None
+            self.pending_write = None
 
 
 # --------------------------------------------------------------------------

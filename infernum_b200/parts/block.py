@@ -6,27 +6,87 @@ here: each output is pushed on the residual stream as a pending delta and the
 next norm kernel folds it in (the reference's optimizer fuses add + rms_norm
 the same way, infernum/src/graph/optimizer.rs:105-174).
 
-Parts of a ``prenorm`` layer: ``norm1``, ``mixer``, ``norm2``, ``ffn``.
+Parts of a ``prenorm`` layer: ``norm1``, ``mixer``, and - unless the layer has no
+feed-forward - ``norm2``, ``ffn``.
+
+``hyper_prenorm``: the same two sub-layers over several residual streams per
+token.  Sub-layer q reads ``u = sum_s in_q[s] x_s``, computes ``y = f(norm_q(u))``
+and writes ``x_t <- sum_s mix_q[s, t] x_s + out_q[t] y`` into all streams at
+once (``mix`` is indexed [from, to]).  The write is not done here either: it is
+pushed on the stream with its coefficients, and the next read-and-norm kernel
+does write, read and norm in one pass over the row.
 """
 
 from __future__ import annotations
 
 from ..errors import ConfigError
-from .base import BLOCKS, Block, ResidualStream
+import torch
+
+from .base import BLOCKS, Block, ResidualStream, WeightSpec
 
 
 @BLOCKS.register("prenorm")
 class PreNormBlock(Block):
     def __init__(self, params, rt, parts):
         super().__init__(params, rt, parts)
-        missing = [r for r in ("norm1", "mixer", "norm2", "ffn") if r not in parts]
+        missing = [r for r in ("norm1", "mixer") if r not in parts]
+        if "ffn" in parts and "norm2" not in parts:
+            missing.append("norm2")
         if missing:
             raise ConfigError(f"prenorm block {params.get('name', '')!r} lacks parts {missing}")
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         p = self.parts
         stream.push(p["mixer"].forward(p["norm1"].forward(stream), ctx, cache))
-        stream.push(p["ffn"].forward(p["norm2"].forward(stream), ctx))
+        if "ffn" in p:
+            stream.push(p["ffn"].forward(p["norm2"].forward(stream), ctx))
+
+
+@BLOCKS.register("hyper_prenorm")
+class HyperPreNormBlock(Block):
+    """Parameters: ``streams``, ``prefix`` (the layer's), ``names`` (default
+    ``hc1`` / ``hc2``: the coefficient tensors are ``<prefix><name>.in`` [S],
+    ``.out`` [S], ``.mix`` [S, S]).  Parts as ``prenorm``; the norms must take a
+    ``read`` mixture (``layernorm`` does)."""
+
+    def __init__(self, params, rt, parts):
+        super().__init__(params, rt, parts)
+        self.streams = int(params["streams"])
+        self.prefix = params.get("prefix", params.get("name", ""))
+        names = params.get("names") or ("hc1", "hc2")
+        missing = [r for r in ("norm1", "mixer") if r not in parts]
+        if "ffn" in parts and "norm2" not in parts:
+            missing.append("norm2")
+        if missing:
+            raise ConfigError(f"hyper_prenorm block {params.get('name', '')!r} lacks parts {missing}")
+        self.subs = [(self.prefix + names[0], "norm1", "mixer")]
+        if "ffn" in parts:
+            self.subs.append((self.prefix + names[1], "norm2", "ffn"))
+        self.coef = {}
+
+    def weight_specs(self):
+        specs = super().weight_specs()
+        S = self.streams
+        for name, _, _ in self.subs:
+            specs[name + ".in"] = WeightSpec((S,), init="norm")
+            specs[name + ".out"] = WeightSpec((S,), init="norm")
+            specs[name + ".mix"] = WeightSpec((S, S), init="normal", std=0.3)
+        return specs
+
+    def bind(self, weights) -> None:
+        super().bind(weights)
+        for name, _, _ in self.subs:
+            self.coef[name] = tuple(weights[name + k].to(torch.float32).contiguous().view(-1)
+                                    for k in (".in", ".mix", ".out"))
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        if stream.residual.dim() != 3 or stream.residual.shape[1] != self.streams:
+            raise ConfigError(f"hyper_prenorm block: the stream does not carry {self.streams} copies")
+        for name, norm, role in self.subs:
+            read, mix, out_coef = self.coef[name]
+            h = self.parts[norm].forward(stream, read=read)
+            y = self.parts[role].forward(h, ctx, cache) if role == "mixer" else self.parts[role].forward(h, ctx)
+            stream.push(y, write=(mix, out_coef))
 
 
 @BLOCKS.register("postnorm")

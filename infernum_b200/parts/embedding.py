@@ -90,6 +90,48 @@ class HashedBigramEmbedding(Embedding):
         return ResidualStream(out, out if act is None else act)
 
 
+@EMBEDDINGS.register("sinusoidal_embedding")
+class SinusoidalEmbedding(Embedding):
+    """``h[t] = E[id_t] + pe(p_t)`` with ``pe(p)[2i] = sin(p * base^(-2i/hidden))`` and
+    ``pe(p)[2i+1] = cos`` of the same angle, ``p`` the token's position in its
+    sequence.  The frequencies are rounded to float32 once (from float64); the
+    angle is their 32-bit product with the position.  ``streams`` > 1 writes that
+    many equal copies per token ([N, streams, hidden]) for layers that keep
+    several residual streams.
+
+    Parameters: ``vocab_size``, ``hidden_size``, ``weight``, ``base`` (default
+    10000), ``streams`` (default 1: a plain [N, hidden] stream).
+    """
+
+    def __init__(self, params, rt: Runtime):
+        super().__init__(params, rt)
+        self.vocab_size = int(params["vocab_size"])
+        self.hidden_size = int(params["hidden_size"])
+        self.weight_name = params["weight"]
+        self.base = float(params.get("base", 10000.0))
+        self.streams = int(params.get("streams") or 0)
+        self.weight: Optional[torch.Tensor] = None
+        self.inv_freq: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.vocab_size, self.hidden_size))}
+
+    def bind(self, weights) -> None:
+        self.weight = weights[self.weight_name].contiguous()
+        i2 = torch.arange(0, self.hidden_size, 2, dtype=torch.float64)
+        inv = torch.pow(torch.tensor(self.base, dtype=torch.float64), -i2 / self.hidden_size)
+        self.inv_freq = inv.to(torch.float32).to(self.weight.device)
+
+    def forward_step(self, ctx, cache) -> ResidualStream:
+        n = ctx.token_ids.numel()
+        S = max(self.streams, 1)
+        out = torch.empty((n, S, self.hidden_size), dtype=torch.float32, device=ctx.token_ids.device)
+        core.embed_sinusoid(ctx.token_ids, ctx.positions, self.weight, self.inv_freq, out, self.rt.err)
+        if self.streams >= 1:
+            return ResidualStream(out, streams=S)
+        return ResidualStream(out.view(n, self.hidden_size))
+
+
 @HEADS.register("linear_head")
 class LinearHead(Part):
     def __init__(self, params, rt: Runtime):
@@ -101,6 +143,8 @@ class LinearHead(Part):
         self.fallback = params.get("fallback")
         # logits <- softcap * tanh(logits / softcap) when given
         self.softcap = float(params["softcap"]) if params.get("softcap") else None
+        # logits <- logits * scale when given
+        self.scale = float(params["scale"]) if params.get("scale") is not None else None
         self.proj: Optional[Linear] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -117,6 +161,8 @@ class LinearHead(Part):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         logits = self.proj(x, out_dtype=torch.float32)
+        if self.scale is not None and self.scale != 1.0:
+            core.scale_inplace(logits, self.scale)
         if self.softcap is not None:
             core.softcap(logits, self.softcap)
         return logits

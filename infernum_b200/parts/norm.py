@@ -98,12 +98,25 @@ class LayerNorm(Norm):
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.weight, self.bias) if t is not None)
 
-    def forward(self, stream: ResidualStream, row_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if stream.pending is not None:
-            stream.flush()
+    def forward(self, stream: ResidualStream, row_idx: Optional[torch.Tensor] = None,
+                read: Optional[torch.Tensor] = None) -> torch.Tensor:
         residual = stream.residual
         n_out = residual.shape[0] if row_idx is None else row_idx.numel()
         out = torch.empty((n_out, self.hidden_size), dtype=self.rt.dtype, device=residual.device)
+        if residual.dim() == 3:
+            # Several streams per token: the pending sub-layer result is written into
+            # them, and the mixture ``sum_s read[s] x_s`` (``read`` None: their sum)
+            # is normed, in one pass.  With a row gather nothing is written back, so
+            # what is pending stays pending.
+            mix, out_coef = stream.pending_write if stream.pending is not None else (None, None)
+            core.hc_norm(residual, stream.pending, mix, out_coef, read, self.weight, self.bias, self.eps, out,
+                         centred=self.centred, row_idx=row_idx)
+            if row_idx is None:
+                stream.pending = None
+                stream.pending_write = None
+            return out
+        if stream.pending is not None:
+            stream.flush()
         core.scale_add_norm(residual, None, self.weight, self.bias, self.eps, out, alpha=1.0,
                             centred=self.centred, store=False, row_idx=row_idx)
         return out

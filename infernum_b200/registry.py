@@ -66,3 +66,5 @@ def _ensure_builtin() -> None:
         from .models import llama  # noqa: F401  (registers itself)
     if "Rugesun" not in _ARCHITECTURES:
         from .models import rugesun  # noqa: F401
+    if "Nadozen" not in _ARCHITECTURES:
+        from .models import nadozen  # noqa: F401

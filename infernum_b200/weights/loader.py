@@ -43,7 +43,7 @@ def check_against_specs(specs: Mapping[str, WeightSpec], table: Mapping[str, Ten
                 missing.append(name)
             continue
         entry = table[src]
-        if tuple(entry.shape) != tuple(spec.shape):
+        if not spec.matches(entry.shape):
             wrong_shape.append((name, tuple(spec.shape), tuple(entry.shape)))
         allowed = _INT_FILE_DTYPES if spec.kind == "int" else _FLOAT_FILE_DTYPES
         if entry.dtype not in allowed:

@@ -67,7 +67,7 @@ def _draw(spec: WeightSpec, key: int, device) -> torch.Tensor:
     arithmetic, so a tensor drawn on the GPU equals the one drawn on the CPU
     bit for bit: a model benchmarked from ``random_model`` can be written out
     with ``write_random_model`` and handed to another implementation."""
-    shape = tuple(spec.shape)
+    shape = spec.concrete_shape
     if spec.kind == "int":
         return torch.zeros(shape, dtype=torch.int32, device=device)
     if spec.init == "zeros":
@@ -144,7 +144,7 @@ def write_random_model(folder: str, config: Mapping[str, Any], seed: int,
         t = _draw(spec, _tensor_key(seed, index[name]), device)
         return (t if spec.kind == "int" else t.to(dtype)).cpu()
 
-    file_specs = [(n, torch.int32 if specs[n].kind == "int" else dtype, specs[n].shape)
+    file_specs = [(n, torch.int32 if specs[n].kind == "int" else dtype, specs[n].concrete_shape)
                   for n in names]
     write_safetensors(os.path.join(folder, "model.safetensors"), file_specs, produce,
                       metadata={"format": "pt", "seed": str(seed)})
