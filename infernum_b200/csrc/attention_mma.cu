@@ -62,6 +62,7 @@ struct Params {
     float* part_o;    // [splits][n_rows][nh][HD]
     float* part_ml;   // [splits][n_rows][nh][2]
     unsigned* err;
+    const float* sink;  // optional [nh]: a logit per head that joins the softmax's denominator only
     int q_stride, out_stride, max_blocks, nh, nkv, page_size, num_pages, window;
     int gs;           // tile mode: query heads of one kv head handled together (<= 16)
     int n_hsub;       // tile mode: ceil((nh / nkv) / gs)
@@ -118,6 +119,18 @@ __device__ __forceinline__ float ld_peer_smem(const float* local, unsigned rank)
     return v;
 }
 // 2^x in 32-bit with the hardware approximation (relative error about 2^-22).
+// What the accumulated values of a row are multiplied by at the end: 1 / l, or,
+// with a sink (a learned logit of the head, not scaled, with no key and no value
+// behind it), 1 / (l + exp(sink - m)).  `m` is the running maximum in the log2
+// domain and `l` the sum of exp2(score - m); m = -inf (nothing seen) gives 0.
+__device__ __forceinline__ float inv_denominator(const float* sink, int head, float m, float l) {
+    if (!sink) return l > 0.f ? 1.f / l : 0.f;
+    const float s2 = sink[head] * 1.4426950408889634f;
+    const float top = fmaxf(m, s2);
+    const float c = exp2f(m - top);
+    return c / (l * c + exp2f(s2 - top));
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -380,7 +393,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         if (my_row[h] < 0) continue;
-        const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+        const float inv = inv_denominator(p.sink, my_head[h], m_run[h], l_run[h]);
         bf16* dst = p.out + (size_t)my_row[h] * p.out_stride + (size_t)my_head[h] * HD;
 #pragma unroll
         for (int nt = 0; nt < HD / 8; ++nt) {
@@ -445,7 +458,7 @@ __device__ __forceinline__ void split_merge(const Params& p, unsigned char* smem
         const int grow = row0 + r, head = g * G + hh;
         if (p.splits == 1) {
             p.out[(size_t)grow * p.out_stride + (size_t)head * HD + d] =
-                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+                __float2bfloat16_rn(acc * inv_denominator(p.sink, head, mx, l));
         } else if (p.cluster_merge) {
             fin[n * HD + d] = acc;
             if (d == 0) {
@@ -486,7 +499,7 @@ __device__ __forceinline__ void split_merge(const Params& p, unsigned char* smem
                 }
             }
             p.out[(size_t)(row0 + r) * p.out_stride + (size_t)(g * G + hh) * HD + d] =
-                __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+                __float2bfloat16_rn(acc * inv_denominator(p.sink, g * G + hh, mx, l));
         }
         cluster_sync_all();  // nobody leaves while a peer may still read its result
     }
@@ -942,7 +955,7 @@ __global__ void attention_combine_kernel(const Params p) {
             }
         }
         p.out[(size_t)row * p.out_stride + (size_t)head * HD + d] =
-            __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+            __float2bfloat16_rn(acc * inv_denominator(p.sink, head, mx, l));
     }
 }
 
@@ -1002,7 +1015,7 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
                                const int* block_tables, int max_blocks, int n_entries, int n_rows,
                                int max_rows_per_entry, int nh, int nkv, int page_size,
                                int num_pages, int window, float scale, int mode, int splits,
-                               void* scratch, long long scratch_bytes, unsigned* err,
+                               void* scratch, long long scratch_bytes, const float* sink, unsigned* err,
                                void* stream) {
     if (n_entries <= 0 || n_rows <= 0) return IB_OK;
     if (!q || !k_pool || !v_pool || !out || !cu_rows || !q_start || !block_tables || !err)
@@ -1023,6 +1036,7 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     p.q_start = q_start;
     p.block_tables = block_tables;
     p.err = err;
+    p.sink = sink;
     p.q_stride = q_stride;
     p.out_stride = out_stride;
     p.max_blocks = max_blocks;

@@ -37,7 +37,7 @@ def lib_for(head_dim: int) -> ctypes.CDLL:
         lib.ib_attention_mma.argtypes = [
             _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
             _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-            _c_float, _c_int, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p]
+            _c_float, _c_int, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p]
         lib.ib_attention_mma.restype = _c_int
         lib.ib_attention_mma_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
         lib.ib_attention_mma_scratch_bytes.restype = _c_ll
@@ -154,8 +154,10 @@ def _step_plan(ctx, G: int, nkv: int, tc_ok: bool, rt) -> dict:
 
 def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=None) -> bool:
     num_pages, nkv, page_size, hd = k_pool.shape
-    if not supported(hd) or sink is not None:
+    if not supported(hd):
         return False
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
+        raise KernelError(f"attention: sink must be contiguous float32 [{n_heads}]")
     core.require_cuda(q, k_pool, v_pool, out, tables)
     if n_heads % nkv:
         raise KernelError(f"attention: {n_heads} heads are not a multiple of {nkv} kv heads")
@@ -163,7 +165,9 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=No
             or k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_mma: bfloat16 tensors with unit inner stride are required")
     G = n_heads // nkv
-    tc_ok = rt.options.get("prompt_attention", "tcgen05") == "tcgen05" and tc_eligible(q, k_pool, out, n_heads, window)
+    # (the tcgen05 prompt kernel knows neither a window nor a sink)
+    tc_ok = (rt.options.get("prompt_attention", "tcgen05") == "tcgen05" and sink is None
+             and tc_eligible(q, k_pool, out, n_heads, window))
     plan = _step_plan(ctx, G, nkv, tc_ok, rt)
     mode, splits = plan["mode"], plan["splits"]
     if (mode & 1) and tc_ok:
@@ -196,6 +200,7 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=No
         out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
         tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
         page_size, num_pages, int(window), float(scale), mode, splits,
-        scratch_ptr, scratch_bytes, rt.err.data_ptr(), core.stream_ptr(q))
+        scratch_ptr, scratch_bytes, sink.data_ptr() if sink is not None else None, rt.err.data_ptr(),
+        core.stream_ptr(q))
     core.check(code, "attention_mma")
     return True
