@@ -103,9 +103,11 @@ def make_folder(folder: str, config: dict, seed: int, sharpen: float = 0.0, drop
         t = tensors[name].float()
         if name.endswith(".q.norm") and sharpen:
             t = t * sharpen
-        elif name.endswith((".left.k", ".left.o", ".left.g", ".right.in", ".right.o", ".mix.r", ".mix.k", ".mix.v",
-                            ".mix.g", ".mix.o", ".mix.w1", ".mix.w2", ".down", ".gate", ".up", "head", "embed")):
+        elif name.endswith((".left.k", ".left.o", ".left.g", ".right.o", ".mix.o", ".down", ".gate", ".up", "head",
+                            "embed")):
             t = t * 6.0
+        elif name.endswith((".right.in", ".mix.r", ".mix.k", ".mix.v", ".mix.g", ".mix.w1", ".mix.w2")):
+            t = t * 3.0   # (what feeds a recurrence: its state sums these over many tokens)
         elif name.endswith(".mix") and ".hc" in name:
             t = t + torch.eye(t.shape[0]) * 0.8   # streams mostly keep themselves
         else:
