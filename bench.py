@@ -116,10 +116,17 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(mhz)}
 
 
-def decode_bytes(model, cache, live_tokens: int) -> int:
-    """Bytes one decode step has to read: every weight it uses once, and the
-    keys and values of the live requests."""
-    return model.step_weight_bytes() + cache.bytes_per_token() * live_tokens
+def decode_bytes(model, cache, live_tokens: int, batch: int = 0) -> int:
+    """Bytes one decode step has to move: every weight it uses once, the keys and
+    values of the live requests (inside their windows), and the requests' fixed-size
+    state, read and written."""
+    per_token = 0
+    el = 2 if model.rt.dtype != __import__("torch").float32 else 4
+    per_request = live_tokens / max(batch, 1)
+    for g in cache.groups:
+        seen = min(per_request, g.spec.window) if g.spec.window > 0 and batch else per_request
+        per_token += g.spec.elements_per_token() * el * len(g.positions) * (seen / per_request if per_request else 1)
+    return int(model.step_weight_bytes() + per_token * live_tokens + 2 * batch * cache.state_bytes_per_request())
 
 
 def prefill_flops(cfg: dict, T: int, layers: int) -> float:
@@ -190,7 +197,7 @@ def time_decode(model, batch, prompt_len, steps, warmup, page_size, seed, clocks
     live = sum(rc.num_tokens for rc in caches) - batch * steps // 2  # mean over the timed steps
     result = {
         "ms_per_step": ms, "tokens_per_s": batch * 1000.0 / ms,
-        "bytes_per_step": decode_bytes(model, cache, live),
+        "bytes_per_step": decode_bytes(model, cache, live, batch),
         "launches_per_step": session.last.launches_per_step,
         "graph": session.last.graph is not None,
         "clocks": clocks.summary(t0, t1) if clocks else None,
@@ -346,6 +353,45 @@ def rugesun_prefill_flops(cfg: dict, T: int) -> float:
     return total + 2.0 * D * cfg["vocab"]
 
 
+def nadozen_config(width, layers, heads, kv_heads, ff, vocab, window=4096, streams=4):
+    """Layers in pairs, each with a gated SiLU feed-forward: sliding-window attention with a
+    sink beside a state space layer (inner width = model width, heads of 64, a state of 128),
+    then wkv time mixing (heads of 64); four residual streams."""
+    par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                    "mask": {"size": window}},
+           "right": {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1},
+           "left_scale": 0.5, "right_scale": 0.5}
+    wkv = {"heads": width // 64, "dim": 64, "decay_rank": 64}
+    dense = {"kind": "dense", "ff": ff}
+    out = [{"type": "parallel", "mixer": par, "mlp": dense} if i % 2 == 0 else
+           {"type": "wkv", "mixer": wkv, "mlp": dense} for i in range(layers)]
+    return {"architecture": "Nadozen", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+            "streams": streams, "layers": out, "max_position": 8192}
+
+
+def nadozen_prefill_flops(cfg: dict, T: int) -> float:
+    """Multiply-adds x 2 of one prompt step: the products, the attention inside its window,
+    and the scans' updates and read-outs of their states."""
+    D, total = cfg["width"], 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "wkv":
+            hk, rank = m["heads"] * m["dim"], m.get("decay_rank") or 64
+            total += 2.0 * T * (5 * D * hk + D * rank + rank * hk) + 2.0 * T * m["heads"] * m["dim"] ** 2 * 3
+        else:
+            a, r = m["left"], m["right"]
+            w = (a.get("mask") or {}).get("size", 0)
+            keys = sum(min(t + 1, w) if w else t + 1 for t in range(T))
+            qd = a["heads"] * a["dim"]
+            inner = r["heads"] * r["vdim"]
+            rows_in = 2 * inner + 2 * r["groups"] * r["state"] + r["heads"]
+            total += 2.0 * T * D * (3 * qd + a["kv_heads"] * a["dim"]) + 4.0 * a["heads"] * a["dim"] * keys
+            total += 2.0 * T * D * (rows_in + inner) + 2.0 * T * r["heads"] * r["state"] * r["vdim"] * 2.5
+        if layer.get("mlp"):
+            total += 6.0 * T * D * layer["mlp"]["ff"]
+    return total + 2.0 * D * cfg["vocab"]
+
+
 DESIGN_SIZES = {
     # name: (width, layers, heads, feed-forward, vocabulary, q_rank, llama kv heads)
     "2b-shape": (2048, 8, 16, 8192, 32000, 768, 4),
@@ -354,7 +400,7 @@ DESIGN_SIZES = {
 
 
 def design_compare(args, peaks) -> dict:
-    """Prefill and decode of the Rugesun decoder at a few sizes, and of the Llama decoder at
+    """Prefill and decode of the chosen design at a few sizes, and of the Llama decoder at
     the same width, depth, heads, feed-forward width and vocabulary."""
     import gc
 
@@ -373,13 +419,18 @@ def design_compare(args, peaks) -> dict:
                  "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": 128,
                  "intermediate_size": ff, "vocab_size": vocab, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
                  "tie_word_embeddings": False, "max_position_embeddings": 8192}
-        rug = rugesun_config(width, layers, heads, ff, vocab, q_rank)
-        for label, cfg in (("rugesun", rug), ("llama", llama)):
+        if args.design == "nadozen":
+            other = nadozen_config(width, layers, heads, kv_heads, ff, vocab)
+            other_flops = nadozen_prefill_flops
+        else:
+            other = rugesun_config(width, layers, heads, ff, vocab, q_rank)
+            other_flops = rugesun_prefill_flops
+        for label, cfg in ((args.design, other), ("llama", llama)):
             if args.only_model and label != args.only_model:
                 continue
             model = ib.random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0", options=dict(opts))
             row = {}
-            flops = (lambda T, c=cfg: rugesun_prefill_flops(c, T)) if label == "rugesun" else \
+            flops = (lambda T, c=cfg: other_flops(c, T)) if label != "llama" else \
                 (lambda T, c=cfg: prefill_flops(c, T, layers))
             for T in (512, 2048):
                 if args.only == "decode":
@@ -480,11 +531,11 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print its numbers (for profiling)")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel")
-    ap.add_argument("--design", choices=["rugesun"], default=None,
+    ap.add_argument("--design", choices=["rugesun", "nadozen"], default=None,
                     help="instead of the default workload: prefill and decode of this design at a few sizes,\n"
                          "beside the Llama decoder at equal sizes; prints one JSON line {\"design\": ...}")
     ap.add_argument("--size", default=None, help="with --design: one of its sizes only")
-    ap.add_argument("--only-model", default=None, help="with --design: 'rugesun' or 'llama' only")
+    ap.add_argument("--only-model", default=None, help="with --design: the design's name or 'llama' only")
     args = ap.parse_args()
 
     if args.impl == "reference":

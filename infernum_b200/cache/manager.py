@@ -228,6 +228,10 @@ class CacheManager:
         el = torch.empty((), dtype=self.dtype).element_size()
         return sum(g.spec.elements_per_token() * el * len(g.positions) for g in self.groups)
 
+    def state_bytes_per_request(self) -> int:
+        """Bytes of fixed-size state one request holds over all scheduled runs."""
+        return sum(st[0].numel() * st.element_size() for st in self._state_tensors)
+
     def free_pages(self) -> List[int]:
         return [g.pool.num_free for g in self.groups]
 

@@ -19,14 +19,38 @@ using namespace ib;
 
 #define IB_MAX_STREAMS 8
 
-template <typename TD, typename TW, typename TO>
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<const unsigned*>(&a);
+    t.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+
+// W = 4: four neighbouring columns a thread (H a multiple of 4, 16-byte loads of the streams);
+// W = 1: any H.  The arithmetic per column and the order of the sums over the streams are the same.
+template <typename TD, typename TW, typename TO, int W>
 __global__ void hc_norm_kernel(float* __restrict__ x, const TD* __restrict__ y, const float* __restrict__ mix,
                                const float* __restrict__ out_coef, const float* __restrict__ read,
                                const TW* __restrict__ weight, const TW* __restrict__ bias, TO* __restrict__ out,
                                const int* __restrict__ row_idx, int S, int H, float eps, int centred,
                                int write_back) {
     pdl_trigger();
-    extern __shared__ float hc_row[];
+    extern __shared__ float4 hc_row4[];
+    float* hc_row = reinterpret_cast<float*>(hc_row4);
     __shared__ float scratch[33];
     __shared__ float s_mix[IB_MAX_STREAMS * IB_MAX_STREAMS], s_out[IB_MAX_STREAMS], s_read[IB_MAX_STREAMS];
     // (the coefficients are weights: no kernel writes them, so they may be read before the wait)
@@ -43,46 +67,89 @@ __global__ void hc_norm_kernel(float* __restrict__ x, const TD* __restrict__ y, 
     const TD* yr = y ? y + (size_t)src * H : nullptr;
 
     float sum = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float old[IB_MAX_STREAMS];
+    for (int i = threadIdx.x * W; i < H; i += blockDim.x * W) {
+        float old[IB_MAX_STREAMS][W];
 #pragma unroll
-        for (int s = 0; s < IB_MAX_STREAMS; ++s) old[s] = s < S ? xr[(size_t)s * H + i] : 0.f;
-        float u = 0.f;
+        for (int s = 0; s < IB_MAX_STREAMS; ++s) {
+            if (s < S) {
+                if (W == 4) load4(xr + (size_t)s * H + i, reinterpret_cast<float(&)[4]>(old[s]));
+                else old[s][0] = xr[(size_t)s * H + i];
+            }
+        }
+        float u[W];
+#pragma unroll
+        for (int k = 0; k < W; ++k) u[k] = 0.f;
         if (yr) {
-            const float yv = to_f32(yr[i]);
+            float yv[W];
+            if (W == 4) load4(yr + i, reinterpret_cast<float(&)[4]>(yv));
+            else yv[0] = to_f32(yr[i]);
 #pragma unroll
             for (int t = 0; t < IB_MAX_STREAMS; ++t) {
                 if (t >= S) break;
-                float nv = 0.f;
+                float nv[W];
 #pragma unroll
-                for (int s = 0; s < IB_MAX_STREAMS; ++s)
-                    if (s < S) nv += s_mix[s * S + t] * old[s];
-                nv += s_out[t] * yv;
-                if (write_back) xr[(size_t)t * H + i] = nv;
-                u += s_read[t] * nv;
+                for (int k = 0; k < W; ++k) nv[k] = 0.f;
+#pragma unroll
+                for (int s = 0; s < IB_MAX_STREAMS; ++s) {
+                    if (s < S) {
+#pragma unroll
+                        for (int k = 0; k < W; ++k) nv[k] += s_mix[s * S + t] * old[s][k];
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < W; ++k) {
+                    nv[k] += s_out[t] * yv[k];
+                    u[k] += s_read[t] * nv[k];
+                }
+                if (write_back) {
+                    if (W == 4) store4(xr + (size_t)t * H + i, reinterpret_cast<const float(&)[4]>(nv));
+                    else xr[(size_t)t * H + i] = nv[0];
+                }
             }
         } else {
 #pragma unroll
-            for (int s = 0; s < IB_MAX_STREAMS; ++s)
-                if (s < S) u += s_read[s] * old[s];
+            for (int s = 0; s < IB_MAX_STREAMS; ++s) {
+                if (s < S) {
+#pragma unroll
+                    for (int k = 0; k < W; ++k) u[k] += s_read[s] * old[s][k];
+                }
+            }
         }
-        hc_row[i] = u;
-        sum += u;
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            hc_row[i + k] = u[k];
+            sum += u[k];
+        }
     }
     if (!out) return;
     float mean = 0.f;
     if (centred) mean = block_sum(sum, scratch) / (float)H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float c = hc_row[i] - mean;
-        ss += c * c;
+    for (int i = threadIdx.x * W; i < H; i += blockDim.x * W) {
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            const float c = hc_row[i + k] - mean;
+            ss += c * c;
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.f / sqrtf(ss / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = (hc_row[i] - mean) * inv * to_f32(weight[i]);
-        if (bias) v += to_f32(bias[i]);
-        out[(size_t)row * H + i] = from_f32<TO>(v);
+    for (int i = threadIdx.x * W; i < H; i += blockDim.x * W) {
+        float wv[W], bv[W], v[W];
+        if (W == 4) {
+            load4(weight + i, reinterpret_cast<float(&)[4]>(wv));
+            if (bias) load4(bias + i, reinterpret_cast<float(&)[4]>(bv));
+        } else {
+            wv[0] = to_f32(weight[i]);
+            if (bias) bv[0] = to_f32(bias[i]);
+        }
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+            v[k] = (hc_row[i + k] - mean) * inv * wv[k];
+            if (bias) v[k] += bv[k];
+        }
+        if (W == 4) store4(out + (size_t)row * H + i, reinterpret_cast<const float(&)[4]>(v));
+        else out[(size_t)row * H + i] = from_f32<TO>(v[0]);
     }
 }
 
@@ -90,20 +157,23 @@ template <typename TD, typename TW, typename TO>
 static int launch_hc(float* x, const void* y, const float* mix, const float* out_coef, const float* read,
                      const void* weight, const void* bias, void* out, const int* row_idx, int n_rows, int S, int H,
                      float eps, int centred, int write_back, cudaStream_t s) {
-    int threads = 256;
-    if (H >= 8192) threads = 1024;
-    else if (H >= 2048) threads = 512;
-    else if (H <= 512) threads = 128;
-    const size_t smem = (size_t)H * sizeof(float);
+    const bool vec = H % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)y & 15) && !((uintptr_t)out & 15) &&
+                     !((uintptr_t)weight & 15) && !((uintptr_t)bias & 15);
+    const int items = vec ? H / 4 : H;
+    int threads = 128;
+    if (items >= 4096) threads = 1024;
+    else if (items >= 1024) threads = 512;
+    else if (items >= 512) threads = 256;
+    const size_t smem = (size_t)H * sizeof(float) + 16;
+    auto kernel = vec ? hc_norm_kernel<TD, TW, TO, 4> : hc_norm_kernel<TD, TW, TO, 1>;
     if (smem > 48 * 1024) {
         if (smem > 200 * 1024) return IB_ERR_TOO_LARGE;
-        cudaError_t e = cudaFuncSetAttribute(hc_norm_kernel<TD, TW, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    cudaError_t le = launch_kernel(hc_norm_kernel<TD, TW, TO>, dim3(n_rows), dim3(threads), smem, s, x,
-                                   (const TD*)y, mix, out_coef, read, (const TW*)weight, (const TW*)bias, (TO*)out,
-                                   row_idx, S, H, eps, centred, write_back);
+    cudaError_t le = launch_kernel(kernel, dim3(n_rows), dim3(threads), smem, s, x, (const TD*)y, mix, out_coef,
+                                   read, (const TW*)weight, (const TW*)bias, (TO*)out, row_idx, S, H, eps, centred,
+                                   write_back);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;

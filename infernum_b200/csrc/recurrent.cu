@@ -154,6 +154,151 @@ IB_EXPORT int ib_causal_conv_silu(const void* x, int x_stride, int act_dtype, co
 }
 
 // ---------------------------------------------------------------------------
+// What the scans read, made in one parallel pass so that the scans themselves only
+// copy: every transcendental of a token is computed here, in 32-bit.
+//
+// ssd_prepare: the causal convolution and SiLU of x | B | C (w null: the rows are
+// taken as they are), written apart in 32-bit and by head, the way the scan
+// fetches them - x [heads][rows][P], (B, C) pairs [groups][rows][state] - and per
+// head (dt, exp(-exp(A_log) dt)) [heads][rows] with dt = softplus(dt_raw + dt_bias).
+template <typename T>
+__global__ void ssd_prepare_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
+                                   const float* __restrict__ b, const float* __restrict__ state,
+                                   long long state_stride, const int* __restrict__ row_entry,
+                                   const int* __restrict__ cu_rows, const int* __restrict__ slot_ids,
+                                   const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ dt_bias,
+                                   const float* __restrict__ a_log, float* __restrict__ xo, float2* __restrict__ bc,
+                                   float2* __restrict__ dd, int inner, int gn, int heads, int taps, int n_rows,
+                                   int P, int state_rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int C = inner + 2 * gn;
+    int first = 0;
+    const float* st = nullptr;
+    if (w) {
+        const int e = row_entry[row];
+        first = cu_rows[e];
+        st = state + (long long)slot_ids[e] * state_stride;
+    }
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C + heads; c += gridDim.y * blockDim.x) {
+        if (c >= C) {
+            const int h = c - C;
+            const float raw = to_f32(dt_raw[(size_t)row * dt_stride + h]) + dt_bias[h];
+            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+            dd[(size_t)h * n_rows + row] = make_float2(dt, expf(-expf(a_log[h]) * dt));
+            continue;
+        }
+        float v;
+        if (w) {
+            float acc = b ? b[c] : 0.f;
+            for (int j = 0; j < taps; ++j) {
+                const int src = row - (taps - 1 - j);
+                float in;
+                if (src >= first) in = to_f32(x[(size_t)src * x_stride + c]);
+                else in = st[(size_t)(taps - 1 - (first - src)) * C + c];
+                acc += w[(size_t)c * taps + j] * in;
+            }
+            v = silu_f(acc);
+        } else {
+            v = to_f32(x[(size_t)row * x_stride + c]);
+        }
+        if (c < inner) {
+            xo[((size_t)(c / P) * n_rows + row) * P + c % P] = v;
+        } else {
+            const int k = c < inner + gn ? c - inner : c - inner - gn;
+            float2* dst = bc + ((size_t)(k / state_rows) * n_rows + row) * state_rows + k % state_rows;
+            if (c < inner + gn) dst->x = v;
+            else dst->y = v;
+        }
+    }
+}
+
+IB_EXPORT int ib_ssd_prepare(const void* x, int x_stride, int act_dtype, const float* w, const float* b,
+                             float* state, long long state_stride, const int* row_entry, const int* cu_rows,
+                             const int* slot_ids, const void* dt_raw, int dt_stride, const float* dt_bias,
+                             const float* a_log, float* xo, void* bc, void* dd, int n_rows, int n_entries,
+                             int inner, int gn, int heads, int state_rows, int taps, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !dt_raw || !dt_bias || !a_log || !xo || !bc || !dd || inner <= 0 || gn <= 0 || heads <= 0 ||
+        inner % heads || state_rows <= 0 || gn % state_rows)
+        return IB_ERR_BAD_ARG;
+    const int P = inner / heads;
+    if (w && (!state || !row_entry || !cu_rows || !slot_ids || taps <= 0 || taps > IB_MAX_TAPS || n_entries <= 0))
+        return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int C = inner + 2 * gn;
+    const int threads = 128;
+    const int gy = min(64, (C + heads + threads - 1) / threads);
+    cudaError_t le;
+    if (act_dtype == 0) {
+        le = launch_kernel(ssd_prepare_kernel<float>, dim3(n_rows, gy), dim3(threads), 0, s, (const float*)x, x_stride,
+                           w, b, (const float*)state, state_stride, row_entry, cu_rows, slot_ids,
+                           (const float*)dt_raw, dt_stride, dt_bias, a_log, xo, (float2*)bc, (float2*)dd, inner, gn,
+                           heads, taps, n_rows, P, state_rows);
+        if (le == cudaSuccess && w && taps > 1)
+            le = launch_kernel(conv_state_kernel<float>, dim3(n_entries, gy), dim3(threads), 0, s, (const float*)x,
+                               x_stride, state, state_stride, cu_rows, slot_ids, C, taps);
+    } else if (act_dtype == 1) {
+        le = launch_kernel(ssd_prepare_kernel<bf16>, dim3(n_rows, gy), dim3(threads), 0, s, (const bf16*)x, x_stride,
+                           w, b, (const float*)state, state_stride, row_entry, cu_rows, slot_ids,
+                           (const bf16*)dt_raw, dt_stride, dt_bias, a_log, xo, (float2*)bc, (float2*)dd, inner, gn,
+                           heads, taps, n_rows, P, state_rows);
+        if (le == cudaSuccess && w && taps > 1)
+            le = launch_kernel(conv_state_kernel<bf16>, dim3(n_entries, gy), dim3(threads), 0, s, (const bf16*)x,
+                               x_stride, state, state_stride, cu_rows, slot_ids, C, taps);
+    } else {
+        return IB_ERR_UNSUPPORTED;
+    }
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// wkv_prepare: per key channel (r, k, w, u k) with w = exp(-exp(z + w0)), and v in 32-bit, both
+// by head: [heads][rows][K].
+template <typename T>
+__global__ void wkv_prepare_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, int ld,
+                                   const float* __restrict__ z, const float* __restrict__ w0,
+                                   const float* __restrict__ u, float4* __restrict__ f, float* __restrict__ vo,
+                                   int hk, int K, int n_rows, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t row = idx / hk;
+    const int c = (int)(idx % hk);
+    const float rr = to_f32(r[row * ld + c]);
+    const float kk = to_f32(k[row * ld + c]);
+    const float w = expf(-expf(z[idx] + w0[c]));
+    const size_t at = ((size_t)(c / K) * n_rows + row) * K + c % K;
+    f[at] = make_float4(rr, kk, w, u[c] * kk);
+    vo[at] = to_f32(v[row * ld + c]);
+}
+
+IB_EXPORT int ib_wkv_prepare(const void* r, const void* k, const void* v, int ld, int act_dtype, const float* z,
+                             const float* w0, const float* u, void* f, float* vo, int n_rows, int hk, int K,
+                             void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!r || !k || !v || !z || !w0 || !u || !f || !vo || hk <= 0 || K <= 0 || hk % K) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)n_rows * hk;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(wkv_prepare_kernel<float>, dim3(grid), dim3(256), 0, s, (const float*)r, (const float*)k,
+                           (const float*)v, ld, z, w0, u, (float4*)f, vo, hk, K, n_rows, total);
+    else if (act_dtype == 1)
+        le = launch_kernel(wkv_prepare_kernel<bf16>, dim3(grid), dim3(256), 0, s, (const bf16*)r, (const bf16*)k,
+                           (const bf16*)v, ld, z, w0, u, (float4*)f, vo, hk, K, n_rows, total);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
 // One warp per (row, head): out = o / sqrt(mean_head(o^2) + eps) * w * silu(g).
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ g, int g_stride,

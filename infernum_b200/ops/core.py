@@ -120,6 +120,14 @@ def core_lib() -> ctypes.CDLL:
         lib.ib_qk_norm_append.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p,
                                           _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                                           _c_int, _c_int, _c_void_p, _c_void_p]
+        lib.ib_ssd_prepare.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p,
+                                       _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                       _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                       _c_void_p]
+        lib.ib_wkv_prepare.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                       _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_ssd_prepare.restype = _c_int
+        lib.ib_wkv_prepare.restype = _c_int
         lib.ib_pointwise.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float,
                                      _c_void_p]
         for fn in ("ib_hc_norm", "ib_embed_sinusoid", "ib_scale_inplace", "ib_token_shift", "ib_causal_conv_silu",

@@ -30,12 +30,10 @@ def lib_for(rows: int) -> ctypes.CDLL:
         if not 1 <= rows <= MAX_ROWS:
             raise KernelError(f"recurrent scan: a state of {rows} rows per head is outside 1..{MAX_ROWS}")
         lib = load_module(f"scan_r{rows}", ["scan.cu"], [f"-DIB_ROWS={rows}"])
-        lib.ib_wkv_scan.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
-                                    _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                                    _c_void_p]
-        lib.ib_ssd_scan.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
-                                    _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                                    _c_int, _c_void_p]
+        lib.ib_wkv_scan.argtypes = [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p,
+                                    _c_int, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_ssd_scan.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_ll, _c_void_p,
+                                    _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]
         for fn in ("ib_wkv_scan", "ib_ssd_scan", "ib_scan_rows", "ib_scan_split"):
             getattr(lib, fn).restype = _c_int
         if lib.ib_scan_rows() != rows:
@@ -45,16 +43,17 @@ def lib_for(rows: int) -> ctypes.CDLL:
 
 
 def choose_col_slices(n_entries: int, heads: int, cols: int, split: int, sm_count: int) -> int:
-    """Into how many CTAs the columns of a head's state are cut.  A CTA walks its
-    entry's tokens one after the other, so the scan's time is the longest entry's
-    whatever the grid; slices shorten it by giving every CTA fewer columns, while
-    the grid still fits the SMs in one round and a CTA keeps at least two warps.
-    A CTA takes at most 512 threads.  The result does not change any number: a
-    column's arithmetic is the same in every slicing."""
+    """Into how many CTAs the columns of a head's state are cut.  The warps of a
+    scan are as many as its columns times the lanes of a column, whatever the
+    slicing; slices only spread them over the SMs.  Every CTA fetches the whole of
+    its head's per-token factors, so a head is cut no further than it takes to give
+    most SMs a CTA, and a CTA keeps at least one warp and at most 512 threads.
+    The result does not change any number: a column's arithmetic is the same in
+    every slicing."""
     slices = 1
     while cols % (slices * 2) == 0 and (
             (cols // slices) * split > 512
-            or (n_entries * heads * slices * 2 <= 2 * sm_count and (cols // (slices * 2)) * split >= 64)):
+            or (4 * n_entries * heads * slices < 3 * sm_count and (cols // (slices * 2)) * split >= 32)):
         slices *= 2
     if (cols // slices) * split > 512:
         # (no power of two cuts it small enough: take the smallest divisor that does)
@@ -72,10 +71,12 @@ def _state_ptr(state: torch.Tensor, offset: int):
 
 def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, u: torch.Tensor,
              state: torch.Tensor, state_offset: int, ctx, out: torch.Tensor, heads: int, rt) -> None:
-    """Per head, with S [K, K] from ``state[slot, offset:]``:
+    """Per head, with S [K, K] from ``state[slot, offset:]`` (stored column by column):
     ``o_t = (S + diag(u) k_t v_t^T)^T r_t``, then ``S <- diag(w_t) S + k_t v_t^T``
     with ``w_t = exp(-exp(z_t + w0))``.  ``r, k, v`` [N, heads * K] (activation
-    dtype, one row stride), ``z`` float32 [N, heads * K], ``out`` float32."""
+    dtype, one row stride), ``z`` float32 [N, heads * K], ``out`` float32.
+    Two kernels: a parallel pass that makes every token's factors in 32-bit, and
+    the scan that walks each entry's tokens in order."""
     core.require_cuda(r, k, v, z, w0, u, state, out)
     N, HK = r.shape
     K = HK // heads
@@ -89,27 +90,36 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         if t.dtype != torch.float32 or t.numel() != HK or not t.is_contiguous():
             raise KernelError(f"wkv_scan: {name} must be contiguous float32 with {HK} values")
     lib = lib_for(K)
+    factors = torch.empty((N, HK, 4), dtype=torch.float32, device=r.device)
+    v32 = torch.empty((N, HK), dtype=torch.float32, device=r.device)
+    core.check(core.core_lib().ib_wkv_prepare(r.data_ptr(), k.data_ptr(), v.data_ptr(), r.stride(0),
+                                              core.dtype_code(r.dtype), z.data_ptr(), w0.data_ptr(), u.data_ptr(),
+                                              factors.data_ptr(), v32.data_ptr(), N, HK, K, core.stream_ptr(r)),
+               "wkv_prepare")
     ptr, stride = _state_ptr(state, state_offset)
     sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
     slices = choose_col_slices(ctx.n_entries, heads, K, lib.ib_scan_split(), sm)
-    core.check(lib.ib_wkv_scan(r.data_ptr(), k.data_ptr(), v.data_ptr(), r.stride(0), core.dtype_code(r.dtype),
-                               z.data_ptr(), w0.data_ptr(), u.data_ptr(), ptr, stride, ctx.cu_rows.data_ptr(),
+    core.check(lib.ib_wkv_scan(factors.data_ptr(), v32.data_ptr(), N, ptr, stride, ctx.cu_rows.data_ptr(),
                                ctx.slot_ids.data_ptr(), out.data_ptr(), ctx.n_entries, heads, K, slices,
                                core.stream_ptr(r)), "wkv_scan")
 
 
 def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
              state: torch.Tensor, state_offset: int, ctx, out: torch.Tensor, heads: int, groups: int,
-             state_rows: int, vdim: int, rt) -> None:
-    """Per head, with S [state_rows, vdim] from ``state[slot, offset:]``:
+             state_rows: int, vdim: int, rt, conv=None) -> None:
+    """Per head, with S [state_rows, vdim] from ``state[slot, offset:]`` (stored column by column):
     ``S <- exp(-exp(a_log) dt) S + dt B_t x_t^T``, ``y_t = S^T C_t + d_skip x_t``,
     ``dt = softplus(dt_raw + dt_bias)``.  ``xbc`` [N, heads*vdim + 2*groups*state_rows]
-    holds x, B and C side by side; ``dt`` [N, heads] may be a view of wider rows;
-    ``out`` float32 [N, heads * vdim]."""
+    holds x, B and C side by side; ``dt`` [N, heads]; both may be views of wider
+    rows; ``out`` float32 [N, heads * vdim].  ``conv`` = (weight [C, taps], bias
+    [C] or None, offset of the convolution's inputs in the state): x, B and C
+    first pass a causal convolution per channel and SiLU, whose last ``taps - 1``
+    inputs are carried in the state.  Two kernels as for ``wkv_scan``: the parallel
+    pass (with the convolution) and the scan."""
     core.require_cuda(xbc, dt, dt_bias, a_log, d_skip, state, out)
     N = xbc.shape[0]
-    inner = heads * vdim
-    if xbc.shape[1] != inner + 2 * groups * state_rows or xbc.stride(1) != 1 or dt.shape != (N, heads) \
+    inner, gn = heads * vdim, groups * state_rows
+    if xbc.shape[1] != inner + 2 * gn or xbc.stride(1) != 1 or dt.shape != (N, heads) \
             or dt.stride(1) != 1 or dt.dtype != xbc.dtype or heads % groups:
         raise KernelError("ssd_scan: xbc [N, inner + 2 groups state] and dt [N, heads] of one dtype do not fit")
     if out.shape != (N, inner) or out.dtype != torch.float32 or not out.is_contiguous():
@@ -118,10 +128,28 @@ def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
         if t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous():
             raise KernelError(f"ssd_scan: {name} must be contiguous float32 [{heads}]")
     lib = lib_for(state_rows)
+    x32 = torch.empty((N, inner), dtype=torch.float32, device=xbc.device)
+    bc = torch.empty((N, gn, 2), dtype=torch.float32, device=xbc.device)
+    dd = torch.empty((N, heads, 2), dtype=torch.float32, device=xbc.device)
+    w = b = None
+    taps, conv_ptr, conv_stride = 1, None, 0
+    if conv is not None:
+        w, b, conv_offset = conv
+        taps = w.shape[1]
+        if w.dtype != torch.float32 or w.shape[0] != inner + 2 * gn or not w.is_contiguous() or (
+                b is not None and (b.dtype != torch.float32 or b.numel() != inner + 2 * gn or not b.is_contiguous())):
+            raise KernelError("ssd_scan: the convolution's weight [C, taps] and bias [C] must be contiguous float32")
+        conv_ptr, conv_stride = _state_ptr(state, conv_offset)
+    core.check(core.core_lib().ib_ssd_prepare(
+        xbc.data_ptr(), xbc.stride(0), core.dtype_code(xbc.dtype), w.data_ptr() if w is not None else None,
+        b.data_ptr() if b is not None else None, conv_ptr, conv_stride, ctx.row_entry.data_ptr(),
+        ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(), dt.data_ptr(), dt.stride(0), dt_bias.data_ptr(),
+        a_log.data_ptr(), x32.data_ptr(), bc.data_ptr(), dd.data_ptr(), N, ctx.n_entries, inner, gn, heads, state_rows,
+        taps,
+        core.stream_ptr(xbc)), "ssd_prepare")
     ptr, stride = _state_ptr(state, state_offset)
     sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
     slices = choose_col_slices(ctx.n_entries, heads, vdim, lib.ib_scan_split(), sm)
-    core.check(lib.ib_ssd_scan(xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0), core.dtype_code(xbc.dtype),
-                               dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), ptr, stride,
+    core.check(lib.ib_ssd_scan(x32.data_ptr(), bc.data_ptr(), dd.data_ptr(), N, d_skip.data_ptr(), ptr, stride,
                                ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(), out.data_ptr(), ctx.n_entries, heads,
                                groups, vdim, slices, core.stream_ptr(xbc)), "ssd_scan")

@@ -183,11 +183,10 @@ class SsdMixer(Mixer):
         z = zx[:, : self.inner]
         xbc_raw = zx[:, self.inner: self.inner + self.channels]
         dt = zx[:, self.inner + self.channels:]
-        xbc = torch.empty((N, self.channels), dtype=x.dtype, device=x.device)
-        core.causal_conv_silu(xbc_raw, self.conv_w, self.conv_b, state, self.off_conv, ctx, xbc)
         y = torch.empty((N, self.inner), dtype=torch.float32, device=x.device)
-        scan_ops.ssd_scan(xbc, dt, self.dt_bias, self.a_log, self.d_skip, state, 0, ctx, y, self.heads, self.groups,
-                          self.state_rows, self.vdim, self.rt)
+        # (the convolution runs in the pass that prepares the scan's inputs: its result stays 32-bit)
+        scan_ops.ssd_scan(xbc_raw, dt, self.dt_bias, self.a_log, self.d_skip, state, 0, ctx, y, self.heads, self.groups,
+                          self.state_rows, self.vdim, self.rt, conv=(self.conv_w, self.conv_b, self.off_conv))
         out = torch.empty((N, self.inner), dtype=x.dtype, device=x.device)
         core.gated_group_norm(y, z, self.norm, self.norm_groups, self.eps, out)
         return self.w_o(out)
