@@ -75,12 +75,26 @@ struct Params {
     const int* q_start;
     const int* block_tables;
     unsigned* err;
+    const float* sink;  // optional [nh]: a logit per head that joins the softmax's denominator only
     int out_stride, max_blocks, nh, nkv, page_size, num_pages;
     int small_rows;     // entries with rows * min(group, 8) <= small_rows belong to split mode
     int splits;         // CTAs (one cluster) that share the keys of a row tile: 1, 2 or 4
     int entry_offset;   // the grid's y starts at this entry (those before it are all split mode's)
     float scale_log2;
 };
+
+// What a row's accumulated values are multiplied by at the end: 1 / l, or, with a sink (a learned
+// logit of the head, not scaled, with no key and no value), 1 / (l + exp(sink - m)).  `m2` is the
+// row's reference maximum in the exponent's units (score * scale * log2 e), `l` the sum of
+// exp2(score - reference); nothing seen (l = 0, m2 = -inf or unused) gives 0.
+__device__ __forceinline__ float inv_denominator(const float* sink, int head, float m2, float l) {
+    if (!sink) return l > 0.f ? 1.f / l : 0.f;
+    if (!(l > 0.f)) return 0.f;
+    const float s2 = sink[head] * 1.4426950408889634f;
+    const float top = fmaxf(m2, s2);
+    const float c = exp2f(m2 - top);
+    return c / (l * c + exp2f(s2 - top));
+}
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool elect_one() {
@@ -562,7 +576,7 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
             l_keep = l_run;
         }
         if (S == 1) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            const float inv = inv_denominator(p.sink, g * G + h, m_run * p.scale_log2, l_run);
             bf16* dst = valid ? p.out + (size_t)(row0 + r_begin + r) * p.out_stride + (size_t)(g * G + h) * HD : nullptr;
 #pragma unroll
             for (int c = 0; c < HD; c += 16) {
@@ -631,7 +645,7 @@ __device__ __forceinline__ void attention_body(const CUtensorMap& map_q, const C
                 w[q - 1] = m_peer[q - 1] > -INFINITY ? fast_exp2(fmaf(m_peer[q - 1], p.scale_log2, -base)) : 0.f;
                 l_all += w[q - 1] * l_peer[q - 1];
             }
-            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+            const float inv = inv_denominator(p.sink, g * G + h, base, l_all);
             bf16* dst = valid ? p.out + (size_t)(row0 + r_begin + r) * p.out_stride + (size_t)(g * G + h) * HD : nullptr;
 #pragma unroll 1
             for (int c = 0; c < HD; c += 16) {
@@ -713,12 +727,14 @@ IB_EXPORT int ib_attention_tc_head_dim() { return HD; }
 // would leave most SMs idle.  `entry_offset`: the first entry the grid covers (a
 // step lists its decoded tokens first; no CTA is launched for them here).
 // Needs: bf16, head size 64 or 128, (heads / kv_heads) a divisor of 128,
-// page_size a multiple of 8 that divides 64, no window, 16-byte aligned q rows.
+// page_size a multiple of 8 that divides 64, no window (or one that no row of the step
+// reaches beyond), 16-byte aligned q rows.  `sink` (optional, float32 [nh]) adds exp(sink[head])
+// to each softmax denominator.
 IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, const void* v_pool, void* out,
                               int out_stride, const int* cu_rows, const int* q_start, const int* block_tables,
                               int max_blocks, int n_entries, int n_rows, int max_rows_per_entry, int nh, int nkv,
                               int page_size, int num_pages, float scale, int small_rows, int splits,
-                              int entry_offset, unsigned* err, void* stream) {
+                              int entry_offset, const float* sink, unsigned* err, void* stream) {
     if (n_entries <= 0 || n_rows <= 0) return IB_OK;
     if (!q || !k_pool || !v_pool || !out || !cu_rows || !q_start || !block_tables || !err) return IB_ERR_BAD_ARG;
     if (nh <= 0 || nkv <= 0 || nh % nkv || (splits != 1 && splits != 2 && splits != 4) || entry_offset < 0 ||
@@ -762,6 +778,7 @@ IB_EXPORT int ib_attention_tc(const void* q, int q_stride, const void* k_pool, c
     p.q_start = q_start;
     p.block_tables = block_tables;
     p.err = err;
+    p.sink = sink;
     p.out_stride = out_stride;
     p.max_blocks = max_blocks;
     p.nh = nh;

@@ -56,19 +56,21 @@ def tc_lib_for(head_dim: int) -> ctypes.CDLL:
         lib.ib_attention_tc.argtypes = [
             _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
-            _c_void_p, _c_void_p]
+            _c_void_p, _c_void_p, _c_void_p]
         lib.ib_attention_tc.restype = _c_int
         _tc_libs[head_dim] = lib
     return lib
 
 
-def tc_eligible(q, k_pool, out, n_heads: int, window: int) -> bool:
+def tc_eligible(q, k_pool, out, n_heads: int, window: int, max_kv_len: int = 0) -> bool:
     """Whether the tcgen05 prompt kernel takes this layer: head size 64 or 128,
-    the head group a divisor of 128, pages of 8, 16, 32 or 64 tokens, no window,
-    16-byte aligned rows."""
+    the head group a divisor of 128, pages of 8, 16, 32 or 64 tokens, no window
+    (or one at least as long as the longest request of the step, ``max_kv_len``,
+    which then hides nothing), 16-byte aligned rows."""
     _, nkv, page_size, hd = k_pool.shape
     G = n_heads // nkv
-    return (hd in (64, 128) and window <= 0 and 128 % G == 0 and page_size % 8 == 0
+    no_window = window <= 0 or (max_kv_len > 0 and window >= max_kv_len)
+    return (hd in (64, 128) and no_window and 128 % G == 0 and page_size % 8 == 0
             and 64 % page_size == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
             and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
@@ -156,6 +158,8 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=No
     num_pages, nkv, page_size, hd = k_pool.shape
     if not supported(hd):
         return False
+    if q.stride(0) % 2 or out.stride(0) % 2 or q.data_ptr() % 4 or out.data_ptr() % 4:
+        return False  # (rows of an odd length, as a view of a wider product may have: the plain kernel takes them)
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
         raise KernelError(f"attention: sink must be contiguous float32 [{n_heads}]")
     core.require_cuda(q, k_pool, v_pool, out, tables)
@@ -165,9 +169,8 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=No
             or k_pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_mma: bfloat16 tensors with unit inner stride are required")
     G = n_heads // nkv
-    # (the tcgen05 prompt kernel knows neither a window nor a sink)
-    tc_ok = (rt.options.get("prompt_attention", "tcgen05") == "tcgen05" and sink is None
-             and tc_eligible(q, k_pool, out, n_heads, window))
+    tc_ok = (rt.options.get("prompt_attention", "tcgen05") == "tcgen05"
+             and tc_eligible(q, k_pool, out, n_heads, window, ctx.max_kv_len))
     plan = _step_plan(ctx, G, nkv, tc_ok, rt)
     mode, splits = plan["mode"], plan["splits"]
     if (mode & 1) and tc_ok:
@@ -178,7 +181,8 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=No
             out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
             tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
             page_size, num_pages, float(scale), 8 if (mode & 2) else -1, plan["prompt_splits"],
-            plan["first_prompt_entry"], rt.err.data_ptr(), core.stream_ptr(q))
+            plan["first_prompt_entry"], sink.data_ptr() if sink is not None else None, rt.err.data_ptr(),
+            core.stream_ptr(q))
         core.check(code, "attention_tcgen05")
         if not (mode & 2):
             return True

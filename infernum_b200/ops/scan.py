@@ -47,18 +47,19 @@ def choose_col_slices(n_entries: int, heads: int, cols: int, split: int, sm_coun
     scan are as many as its columns times the lanes of a column, whatever the
     slicing; slices only spread them over the SMs.  Every CTA fetches the whole of
     its head's per-token factors, so a head is cut no further than it takes to give
-    most SMs a CTA, and a CTA keeps at least one warp and at most 512 threads.
+    most SMs a CTA, and a CTA keeps at least one warp, at most 512 threads and at
+    most 128 columns (whose values it stages in shared memory).
     The result does not change any number: a column's arithmetic is the same in
     every slicing."""
     slices = 1
     while cols % (slices * 2) == 0 and (
-            (cols // slices) * split > 512
+            (cols // slices) * split > 512 or cols // slices > 128
             or (4 * n_entries * heads * slices < 3 * sm_count and (cols // (slices * 2)) * split >= 32)):
         slices *= 2
-    if (cols // slices) * split > 512:
+    if (cols // slices) * split > 512 or cols // slices > 128:
         # (no power of two cuts it small enough: take the smallest divisor that does)
         for s in range(slices + 1, cols + 1):
-            if cols % s == 0 and (cols // s) * split <= 512:
+            if cols % s == 0 and (cols // s) * split <= 512 and cols // s <= 128:
                 return s
     return slices
 

@@ -119,6 +119,6 @@ def test_slicing_of_a_scans_columns():
     assert choose_col_slices(1, 4, 64, 4, 148) > 1
     assert choose_col_slices(64, 32, 64, 4, 148) == 1
     # never more than 512 threads, always a divisor
-    for cols, split in ((256, 4), (192, 8), (48, 4), (7, 1), (250, 4)):
+    for cols, split in ((256, 4), (192, 8), (48, 4), (7, 1), (250, 4), (509, 1), (384, 1)):
         s = choose_col_slices(1000, 64, cols, split, 148)
-        assert cols % s == 0 and (cols // s) * split <= 512
+        assert cols % s == 0 and (cols // s) * split <= 512 and cols // s <= 128

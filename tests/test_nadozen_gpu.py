@@ -328,7 +328,7 @@ def cuts_of(T, sizes):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("S,H", [(4, 96), (1, 40), (3, 1000), (8, 64)])
+@pytest.mark.parametrize("S,H", [(4, 96), (1, 40), (3, 1000), (8, 64), (2, 90), (5, 7)])
 def test_streams_write_read_and_norm_in_one_pass(dtype, S, H):
     from infernum_b200.ops import core
     g = torch.Generator().manual_seed(S * H)
@@ -661,16 +661,23 @@ def test_keys_far_away_at_page_borders_and_the_first_tokens_with_a_sink(dtype, o
 
 
 @pytest.mark.parametrize("dtype,options", KERNELS)
-def test_a_sink_that_dominates_takes_the_weight_away_and_counts_once(dtype, options):
+@pytest.mark.parametrize("kv_heads,hd,window", [(2, 32, 0), (2, 128, 0), (8, 64, 0), (2, 64, 4000), (4, 128, 1500)])
+def test_a_sink_that_dominates_takes_the_weight_away_and_counts_once(dtype, options, kv_heads, hd, window):
+    """Also head sizes and windows with which prompts go to the tcgen05 kernel (no window, or one
+    that no request of the step is longer than)."""
     tol = 1e-5 if dtype == "float32" else 2e-2
-    heads, kv_heads, hd = 8, 2, 32
+    heads = 8
     # head 0: a sink far above every score (the output vanishes); head 1: far below (as without one);
     # many keys, so that a sink counted once per key tile or once per slice would show
     sinks = [30.0, -30.0, 3.0, 1.0, 0.0, -2.0, 5.0, 2.5]
-    out, ref, _, _ = attention_case(dtype, heads, kv_heads, hd, 16, [1500, 300, 70], [1, 100, 70], 0, [], sinks,
+    out, ref, _, _ = attention_case(dtype, heads, kv_heads, hd, 16, [1500, 300, 70], [1, 100, 70], window, [], sinks,
                                     options=options)
     assert rel_err(out, ref) < tol
     assert float(out[:, 0].abs().max()) < 1e-3
+    # a long portion behind a long prefix (the prompt kernel cuts its keys over a cluster) beside decoded tokens
+    out, ref, _, _ = attention_case(dtype, heads, kv_heads, hd, 16, [1400, 9, 800], [256, 1, 1], window,
+                                    [(0, 1399, 2), (0, 1200, 1199)], sinks, seed=3, options=options)
+    assert rel_err(out, ref) < tol
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
