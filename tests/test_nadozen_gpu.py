@@ -677,7 +677,9 @@ def test_a_sink_that_dominates_takes_the_weight_away_and_counts_once(dtype, opti
     # a long portion behind a long prefix (the prompt kernel cuts its keys over a cluster) beside decoded tokens
     out, ref, _, _ = attention_case(dtype, heads, kv_heads, hd, 16, [1400, 9, 800], [256, 1, 1], window,
                                     [(0, 1399, 2), (0, 1200, 1199)], sinks, seed=3, options=options)
-    assert rel_err(out, ref) < tol
+    # (a score near 19 beside sinks of its size: the 32-bit rounding of the score, some 1e-6 of it,
+    # is the relative error of its weight, which the sinks keep from saturating)
+    assert rel_err(out, ref) < (5e-5 if dtype == "float32" else tol)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
