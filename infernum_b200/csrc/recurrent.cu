@@ -34,7 +34,7 @@ __global__ void token_shift_kernel(const T* __restrict__ x, const float* __restr
     const int first = cu_rows[e], last = cu_rows[e + 1] - 1;
     float* prev = state + (long long)slot_ids[e] * state_stride;
     const T* xr = x + (size_t)row * D;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < D; c += gridDim.y * blockDim.x) {
         const float h = to_f32(xr[c]);
         float hp;
         if (row == first) {
@@ -55,13 +55,15 @@ IB_EXPORT int ib_token_shift(const void* x, int act_dtype, const float* mu, floa
     if (n_rows <= 0) return IB_OK;
     if (!x || !mu || !state || !row_entry || !cu_rows || !slot_ids || !out || D <= 0 || M <= 0) return IB_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = D >= 1024 ? 256 : 128;
+    const int threads = 128;
+    // (a column a thread: few rows - decoded tokens - still fill the machine)
+    const dim3 grid(n_rows, min(64, (D + threads - 1) / threads));
     cudaError_t le;
     if (act_dtype == 0)
-        le = launch_kernel(token_shift_kernel<float>, dim3(n_rows), dim3(threads), 0, s, (const float*)x, mu, state,
+        le = launch_kernel(token_shift_kernel<float>, grid, dim3(threads), 0, s, (const float*)x, mu, state,
                            state_stride, row_entry, cu_rows, slot_ids, (float*)out, n_rows, D, M);
     else if (act_dtype == 1)
-        le = launch_kernel(token_shift_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, (const bf16*)x, mu, state,
+        le = launch_kernel(token_shift_kernel<bf16>, grid, dim3(threads), 0, s, (const bf16*)x, mu, state,
                            state_stride, row_entry, cu_rows, slot_ids, (bf16*)out, n_rows, D, M);
     else
         return IB_ERR_UNSUPPORTED;
