@@ -439,6 +439,12 @@ def design_compare(args, peaks) -> dict:
                 row[f"prefill_{T}_tok_s"] = round(r["value"], 1)
                 row[f"prefill_{T}_ms"] = round(r["ms"], 3)
                 row[f"prefill_{T}_frac_of_sustained_bf16"] = round(r["frac"], 4)
+                if T == 512:
+                    # the way Engine runs a prompt that comes alone: replayed from a recording
+                    r = time_prefill(model, cfg, layers, T, args.page_size, peaks, flops=flops, recorded=True)
+                    row["prefill_512_recorded_ms"] = round(r["ms"], 3)
+                    row["prefill_512_recorded_host_ms"] = round(r["host_ms"], 3)
+                    row["prefill_512_recorded_frac_of_sustained_bf16"] = round(r["frac"], 4)
             for b in (1, 8, 64):
                 if args.only == "prefill":
                     break
