@@ -9,7 +9,8 @@
 //                  h_{-1} of an entry's first row is the request's state, which
 //                  then takes the entry's last row
 //   causal conv    c_t[ch] = silu(b[ch] + sum_j w[ch][j] x_{t-(taps-1-j)}[ch]),
-//                  inputs before the entry from the state (the last taps-1 inputs)
+//                  inputs before the entry from the state (the last taps-1 inputs);
+//                  part of the pass that prepares a state space scan's inputs
 //   head norm      out = o / rms_head(o) * w * silu(g)          (rms over one head)
 //   gated norm     v = y * silu(z); out = v / rms_group(v) * w   (rms over a group)
 //   qk norm        q, k <- x / rms(x) * w per head; the normed key and the key
@@ -75,31 +76,6 @@ IB_EXPORT int ib_token_shift(const void* x, int act_dtype, const float* mu, floa
 // ---------------------------------------------------------------------------
 #define IB_MAX_TAPS 16
 
-template <typename T>
-__global__ void causal_conv_silu_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w,
-                                        const float* __restrict__ b, const float* __restrict__ state,
-                                        long long state_stride, const int* __restrict__ row_entry,
-                                        const int* __restrict__ cu_rows, const int* __restrict__ slot_ids,
-                                        T* __restrict__ out, int C, int taps) {
-    pdl_trigger();
-    pdl_wait();
-    const int row = blockIdx.x;
-    const int e = row_entry[row];
-    const int first = cu_rows[e];
-    const float* st = state + (long long)slot_ids[e] * state_stride;  // [taps-1][C], the newest last
-    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
-        float acc = b ? b[c] : 0.f;
-        for (int j = 0; j < taps; ++j) {
-            const int src = row - (taps - 1 - j);
-            float v;
-            if (src >= first) v = to_f32(x[(size_t)src * x_stride + c]);
-            else v = st[(size_t)(taps - 1 - (first - src)) * C + c];
-            acc += w[(size_t)c * taps + j] * v;
-        }
-        out[(size_t)row * C + c] = from_f32<T>(silu_f(acc));
-    }
-}
-
 // The state after the step: the last taps-1 inputs of (old state ++ the entry's rows).
 template <typename T>
 __global__ void conv_state_kernel(const T* __restrict__ x, int x_stride, float* __restrict__ state,
@@ -119,40 +95,6 @@ __global__ void conv_state_kernel(const T* __restrict__ x, int x_stride, float* 
         }
         for (int k = 0; k < taps - 1; ++k) st[(size_t)k * C + c] = nv[k];
     }
-}
-
-IB_EXPORT int ib_causal_conv_silu(const void* x, int x_stride, int act_dtype, const float* w, const float* b,
-                                  float* state, long long state_stride, const int* row_entry, const int* cu_rows,
-                                  const int* slot_ids, void* out, int n_rows, int n_entries, int C, int taps,
-                                  void* stream) {
-    if (n_rows <= 0) return IB_OK;
-    if (!x || !w || !state || !row_entry || !cu_rows || !slot_ids || !out || C <= 0 || taps <= 0 ||
-        taps > IB_MAX_TAPS || n_entries <= 0)
-        return IB_ERR_BAD_ARG;
-    cudaStream_t s = (cudaStream_t)stream;
-    const int threads = 128;
-    const int gy = min(64, (C + threads - 1) / threads);
-    cudaError_t le;
-    if (act_dtype == 0) {
-        le = launch_kernel(causal_conv_silu_kernel<float>, dim3(n_rows, gy), dim3(threads), 0, s, (const float*)x,
-                           x_stride, w, b, (const float*)state, state_stride, row_entry, cu_rows, slot_ids,
-                           (float*)out, C, taps);
-        if (le == cudaSuccess && taps > 1)
-            le = launch_kernel(conv_state_kernel<float>, dim3(n_entries, gy), dim3(threads), 0, s, (const float*)x,
-                               x_stride, state, state_stride, cu_rows, slot_ids, C, taps);
-    } else if (act_dtype == 1) {
-        le = launch_kernel(causal_conv_silu_kernel<bf16>, dim3(n_rows, gy), dim3(threads), 0, s, (const bf16*)x,
-                           x_stride, w, b, (const float*)state, state_stride, row_entry, cu_rows, slot_ids,
-                           (bf16*)out, C, taps);
-        if (le == cudaSuccess && taps > 1)
-            le = launch_kernel(conv_state_kernel<bf16>, dim3(n_entries, gy), dim3(threads), 0, s, (const bf16*)x,
-                               x_stride, state, state_stride, cu_rows, slot_ids, C, taps);
-    } else {
-        return IB_ERR_UNSUPPORTED;
-    }
-    if (le != cudaSuccess) return (int)le;
-    IB_LAUNCH_CHECK();
-    return IB_OK;
 }
 
 // ---------------------------------------------------------------------------

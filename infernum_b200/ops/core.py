@@ -111,8 +111,6 @@ def core_lib() -> ctypes.CDLL:
         lib.ib_scale_inplace.argtypes = [_c_void_p, _c_ll, _c_float, _c_void_p]
         lib.ib_token_shift.argtypes = [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p,
                                        _c_void_p, _c_int, _c_int, _c_int, _c_void_p]
-        lib.ib_causal_conv_silu.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p,
-                                            _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]
         lib.ib_head_norm_gate.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
                                           _c_int, _c_float, _c_void_p]
         lib.ib_gated_group_norm.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int,
@@ -130,7 +128,7 @@ def core_lib() -> ctypes.CDLL:
         lib.ib_wkv_prepare.restype = _c_int
         lib.ib_pointwise.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float,
                                      _c_void_p]
-        for fn in ("ib_hc_norm", "ib_embed_sinusoid", "ib_scale_inplace", "ib_token_shift", "ib_causal_conv_silu",
+        for fn in ("ib_hc_norm", "ib_embed_sinusoid", "ib_scale_inplace", "ib_token_shift",
                    "ib_head_norm_gate", "ib_gated_group_norm", "ib_qk_norm_append", "ib_pointwise"):
             getattr(lib, fn).restype = _c_int
         for fn in ("ib_attention_plain_ex", "ib_gemm_plain_batched", "ib_gated_act", "ib_scale_add_norm",
@@ -884,26 +882,6 @@ def token_shift(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, state_of
     check(core_lib().ib_token_shift(x.data_ptr(), dtype_code(x.dtype), mu.data_ptr(), ptr, stride,
                                     ctx.row_entry.data_ptr(), ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(),
                                     out.data_ptr(), N, D, M, stream_ptr(x)), "token_shift")
-
-
-def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
-                     state_offset: int, ctx, out: torch.Tensor) -> None:
-    """Per channel: out[t] = silu(bias + sum_j weight[:, j] x[t - (taps-1-j)]) inside
-    each request; inputs before the step come from ``state[slot, offset:]``
-    ([taps-1, C], the newest last), which is brought up to date.  ``x`` [N, C] may
-    be a view of wider rows; ``weight`` float32 [C, taps]."""
-    require_cuda(x, weight, bias, state, out)
-    N, C = x.shape
-    taps = weight.shape[1]
-    _f32_vec(weight, C * taps, "causal_conv_silu: weight")
-    _f32_vec(bias, C, "causal_conv_silu: bias")
-    if x.stride(1) != 1 or out.shape != (N, C) or out.dtype != x.dtype or not out.is_contiguous():
-        raise KernelError("causal_conv_silu: x [N, C] with unit inner stride, out contiguous [N, C] of x's dtype")
-    ptr, stride = _state_view(state, state_offset)
-    check(core_lib().ib_causal_conv_silu(x.data_ptr(), x.stride(0), dtype_code(x.dtype), weight.data_ptr(), _ptr(bias),
-                                         ptr, stride, ctx.row_entry.data_ptr(), ctx.cu_rows.data_ptr(),
-                                         ctx.slot_ids.data_ptr(), out.data_ptr(), N, ctx.n_entries, C, taps,
-                                         stream_ptr(x)), "causal_conv_silu")
 
 
 def head_norm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, heads: int, eps: float,

@@ -409,28 +409,6 @@ def test_token_shift_carries_the_last_row_between_steps(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps", [1, 2, 4, 7])
-def test_causal_convolution_across_cuts_shorter_than_its_taps(dtype, taps):
-    from infernum_b200.ops import core
-    g = torch.Generator().manual_seed(taps)
-    C, T, extra = 50, 29, 6
-    wide = torch.randn(T, C + extra, generator=g, dtype=torch.float64).to(dtype)
-    w = torch.randn(C, taps, generator=g, dtype=torch.float64).float()
-    b = torch.randn(C, generator=g, dtype=torch.float64).float()
-    ref = pn.silu(pn.causal_conv(wide[:, 2: 2 + C].double(), w.double(), b.double()))
-    state = torch.zeros(2, 11 + max(taps - 1, 1) * C, dtype=torch.float32, device=DEV)
-    state[0] = 3.0  # another request's slot
-    got = []
-    for at, n in cuts_of(T, [1, 1, 2, 1, 5, 3, 1, 9]):
-        x = wide[at: at + n].to(DEV)[:, 2: 2 + C]  # a view of wider rows
-        out = torch.empty(n, C, dtype=dtype, device=DEV)
-        core.causal_conv_silu(x, w.to(DEV), b.to(DEV), state, 11, Step([n], [1]), out)
-        got.append(out.cpu())
-    assert rel_err(torch.cat(got), ref) < PART_TOL[dtype]
-    assert (state[0] == 3).all() and (state[1, :11] == 0).all()
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,K", [(2, 16), (1, 28), (3, 64), (2, 10), (1, 128)])
 def test_wkv_scan_in_portions_and_batches_against_the_recurrence(dtype, heads, K):
     from infernum_b200.ops import scan
@@ -472,9 +450,11 @@ def test_wkv_scan_in_portions_and_batches_against_the_recurrence(dtype, heads, K
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,groups,N,P", [(4, 2, 20, 12), (1, 1, 10, 20), (3, 3, 14, 6), (2, 1, 128, 24),
-                                               (8, 2, 64, 32)])
-def test_ssd_scan_in_portions_and_batches_against_the_recurrence(dtype, heads, groups, N, P):
+@pytest.mark.parametrize("heads,groups,N,P,taps", [(4, 2, 20, 12, 0), (1, 1, 10, 20, 1), (3, 3, 14, 6, 2),
+                                                    (2, 1, 128, 24, 4), (8, 2, 64, 32, 0), (2, 2, 16, 8, 7)])
+def test_ssd_scan_in_portions_and_batches_against_the_recurrence(dtype, heads, groups, N, P, taps):
+    """``taps`` > 0: x, B and C first pass the causal convolution and SiLU, whose last inputs are
+    carried in the state across portions shorter than the convolution."""
     from infernum_b200.ops import scan
     g = torch.Generator().manual_seed(heads * N + P)
     T = {"a": 37, "b": 21}
@@ -483,11 +463,16 @@ def test_ssd_scan_in_portions_and_batches_against_the_recurrence(dtype, heads, g
     data = {r: {"xbc": rnd(n, inner + 2 * groups * N).to(dtype), "dt": rnd(n, heads + 3).to(dtype)}
             for r, n in T.items()}
     dt_bias, a_log, d_skip = rnd(heads).float(), (rnd(heads) * 0.5).float(), rnd(heads).float()
+    channels = inner + 2 * groups * N
+    conv_w, conv_b = (rnd(channels, taps) * 0.5).float(), rnd(channels).float()
     ref = {}
     for r, d in data.items():
-        x = d["xbc"][:, :inner].double().view(-1, heads, P)
-        B = d["xbc"][:, inner: inner + groups * N].double().view(-1, groups, N)
-        C = d["xbc"][:, inner + groups * N:].double().view(-1, groups, N)
+        xbc = d["xbc"].double()
+        if taps:
+            xbc = pn.silu(pn.causal_conv(xbc, conv_w.double(), conv_b.double()))
+        x = xbc[:, :inner].view(-1, heads, P)
+        B = xbc[:, inner: inner + groups * N].view(-1, groups, N)
+        C = xbc[:, inner + groups * N:].view(-1, groups, N)
         dt = pn.softplus(d["dt"][:, 1: 1 + heads].double() + dt_bias.double())
         outs = []
         for a in range(heads):
@@ -496,7 +481,9 @@ def test_ssd_scan_in_portions_and_batches_against_the_recurrence(dtype, heads, g
             outs.append(y)
         ref[r] = torch.cat(outs, dim=-1)
     rt = runtime(dtype)
-    state = torch.zeros(3, heads * N * P + 4, dtype=torch.float32, device=DEV)
+    off_conv = heads * N * P + 4
+    state = torch.zeros(3, off_conv + max(taps - 1, 0) * channels + 3, dtype=torch.float32, device=DEV)
+    conv = (conv_w.to(DEV), conv_b.to(DEV), off_conv) if taps else None
     plan = {"a": cuts_of(T["a"], [2, 1, 16, 1, 3, 40]), "b": cuts_of(T["b"], [1, 1, 7, 20])}
     got = {r: [] for r in T}
     while any(plan.values()):
@@ -506,14 +493,15 @@ def test_ssd_scan_in_portions_and_batches_against_the_recurrence(dtype, heads, g
         step = Step([n for _, n in cuts], [1 if r == "a" else 2 for r in live])
         out = torch.empty(step.n_rows, inner, dtype=torch.float32, device=DEV)
         scan.ssd_scan(cat("xbc"), cat("dt")[:, 1: 1 + heads], dt_bias.to(DEV), a_log.to(DEV), d_skip.to(DEV), state, 0,
-                      step, out, heads, groups, N, P, rt)
+                      step, out, heads, groups, N, P, rt, conv=conv)
         at = 0
         for r, (_, n) in zip(live, cuts):
             got[r].append(out[at: at + n].cpu())
             at += n
     for r in T:
         assert rel_err(torch.cat(got[r]), ref[r]) < 2e-5
-    assert (state[0] == 0).all() and (state[:, heads * N * P:] == 0).all()
+    # the slot nobody had, the floats between the matrices and the convolution's inputs, and those behind them
+    assert (state[0] == 0).all() and (state[:, heads * N * P: off_conv] == 0).all() and (state[:, -3:] == 0).all()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
